@@ -1,0 +1,289 @@
+// extern "C" entry points declared in include/asrq_b200.h: argument checks on the host,
+// per-device facts cached once, dispatch to the kernels.  Nothing here allocates device
+// memory or synchronises (asrq_check_status excepted, which says so).
+#include <algorithm>
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "tcgen05.cuh"
+
+namespace asrq {
+
+// kernels (one translation unit each)
+int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+             void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+             size_t workspace_bytes, int sm_count, cudaStream_t stream);
+size_t gemv_workspace_bytes(int64_t N);
+int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                size_t workspace_bytes, int sm_count, cudaStream_t stream);
+int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
+                        cudaStream_t stream);
+int w4a4_gemm_mma(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias, void* y,
+                  int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                  cudaStream_t stream);
+int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias, void* y,
+                 int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream);
+bool w4a4_gemm_tc_supports(int64_t M, int64_t N, int64_t K, int group_size);
+
+// ---- errors -----------------------------------------------------------------------------
+std::string& last_error() {
+  static thread_local std::string s;
+  return s;
+}
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  last_error() = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  char buf[512];
+  snprintf(buf, sizeof(buf), "CUDA error %d (%s) at %s", int(e), cudaGetErrorString(e), what);
+  last_error() = buf;
+  return int(e) > 0 ? int(e) : 1;
+}
+
+// ---- per-device facts ---------------------------------------------------------------------
+struct DeviceFacts {
+  std::once_flag once;
+  int status = ASRQ_ERR_DEVICE;
+  int sm_count = 0;
+  int cc_major = 0;
+};
+static DeviceFacts g_dev[64];
+
+static int device_facts(const DeviceFacts** out) {
+  int dev = 0;
+  ASRQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(ASRQ_ERR_DEVICE, "device index %d out of range", dev);
+  DeviceFacts& f = g_dev[dev];
+  std::call_once(f.once, [&] {
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return;
+    f.cc_major = major;
+    f.sm_count = sms;
+    f.status = (major == 10) ? ASRQ_OK : ASRQ_ERR_DEVICE;
+  });
+  if (f.status != ASRQ_OK)
+    return fail(ASRQ_ERR_DEVICE, "device %d has compute capability %d.x; this library is built for sm_100a only", dev,
+                f.cc_major);
+  *out = &f;
+  return ASRQ_OK;
+}
+
+// ---- tensor maps ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool bf16, uint64_t inner, uint64_t rows,
+                 uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(ASRQ_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : bf16          ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {inner * uint64_t(elem_bytes)};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  if (strides[0] % 16) return fail(ASRQ_ERR_ALIGN, "row pitch %llu is not a multiple of 16 bytes", (unsigned long long)strides[0]);
+  const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ASRQ_ERR_SHAPE, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return ASRQ_OK;
+}
+
+static int check_a16_common(const char* who, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                            void* y, int64_t M, int64_t N, int64_t K, int dtype, void* workspace) {
+  if (!x || !w || !scales || !zeros || !y) return fail(ASRQ_ERR_NULL, "%s: x, w, scales, zeros and y must not be NULL", who);
+  if (!workspace) return fail(ASRQ_ERR_WORKSPACE, "%s: workspace must not be NULL", who);
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "%s: dtype %d", who, dtype);
+  if (M < 0 || N <= 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "%s: M=%lld N=%lld K=%lld", who, (long long)M, (long long)N, (long long)K);
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y) || !aligned16(workspace))
+    return fail(ASRQ_ERR_ALIGN, "%s: x, w, y and workspace must be 16-byte aligned", who);
+  return ASRQ_OK;
+}
+
+// M at or below which LinearQ.forward goes to the skinny kernel.
+constexpr int64_t kGemvMaxM = 32;
+
+}  // namespace asrq
+
+using namespace asrq;
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int asrq_version(void) { return 100; }
+
+const char* asrq_last_error_string(void) { return last_error().c_str(); }
+
+size_t asrq_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
+  (void)M;
+  (void)K;
+  switch (kind) {
+    case ASRQ_WS_A16_GEMV:
+    case ASRQ_WS_LINEARQ:
+      return gemv_workspace_bytes(N);
+    case ASRQ_WS_A16_GEMM:
+    case ASRQ_WS_W4A4_GEMM:
+      return kStatusBytes;
+    default:
+      return 0;
+  }
+}
+
+static int a16_gemv(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                    void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  last_error().clear();
+  int rc = check_a16_common(bits == 4 ? "asrq_w4a16_gemv" : "asrq_w2a16_gemv", x, w, scales, zeros, y, M, N, K, dtype,
+                            workspace);
+  if (rc) return rc;
+  const DeviceFacts* f;
+  if ((rc = device_facts(&f))) return rc;
+  if (M == 0) return ASRQ_OK;
+  return gemv_a16(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
+                  f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+static int a16_gemm(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                    void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  last_error().clear();
+  int rc = check_a16_common(bits == 4 ? "asrq_w4a16_gemm" : "asrq_w2a16_gemm", x, w, scales, zeros, y, M, N, K, dtype,
+                            workspace);
+  if (rc) return rc;
+  const DeviceFacts* f;
+  if ((rc = device_facts(&f))) return rc;
+  if (M == 0) return ASRQ_OK;
+  return gemm_a16_tc(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
+                     f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_w4a16_gemv(const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias, void* y,
+                    int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return a16_gemv(4, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+}
+int asrq_w2a16_gemv(const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias, void* y,
+                    int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return a16_gemv(2, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+}
+int asrq_w4a16_gemm(const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias, void* y,
+                    int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return a16_gemm(4, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+}
+int asrq_w2a16_gemm(const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias, void* y,
+                    int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return a16_gemm(2, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+}
+
+int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                     const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  if (bits != 2 && bits != 4) {
+    last_error().clear();
+    return fail(ASRQ_ERR_SHAPE, "asrq_linearq_a16: bits must be 2 or 4 (got %d)", bits);
+  }
+  const bool tc_ok = N % 128 == 0 && K % 64 == 0 && group_size > 0 && group_size % 64 == 0 && K % group_size == 0;
+  if (M > kGemvMaxM && tc_ok)
+    return a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+  return a16_gemv(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+}
+
+int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
+                             void* stream) {
+  last_error().clear();
+  if (!x || !qa || !sa) return fail(ASRQ_ERR_NULL, "asrq_hadamard_quant_int4: x, qa and sa must not be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_hadamard_quant_int4: dtype %d", dtype);
+  if (M < 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "asrq_hadamard_quant_int4: M=%lld K=%lld", (long long)M, (long long)K);
+  if (!aligned16(x) || !aligned16(qa)) return fail(ASRQ_ERR_ALIGN, "asrq_hadamard_quant_int4: x and qa must be 16-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  return hadamard_quant_int4(x, qa, sa, M, K, hadamard, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_w4a4_gemm(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias, void* y,
+                   int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+  last_error().clear();
+  if (!qa || !sa || !qw || !sw || !y) return fail(ASRQ_ERR_NULL, "asrq_w4a4_gemm: qa, sa, qw, sw and y must not be NULL");
+  if (!workspace || workspace_bytes < kStatusBytes) return fail(ASRQ_ERR_WORKSPACE, "asrq_w4a4_gemm: workspace");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_w4a4_gemm: dtype %d", dtype);
+  if (M < 0 || N <= 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "asrq_w4a4_gemm: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (!aligned16(qa) || !aligned16(qw) || !aligned16(y) || !aligned16(workspace))
+    return fail(ASRQ_ERR_ALIGN, "asrq_w4a4_gemm: qa, qw, y and workspace must be 16-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (M == 0) return ASRQ_OK;
+  if (w4a4_gemm_tc_supports(M, N, K, group_size))
+    return w4a4_gemm_tc(qa, sa, qw, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, workspace_bytes,
+                        f->sm_count, static_cast<cudaStream_t>(stream));
+  return w4a4_gemm_mma(qa, sa, qw, sw, bias, y, acc_dump, M, N, K, group_size, dtype,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int asrq_check_status(void* workspace, void* stream) {
+  last_error().clear();
+  if (!workspace) return fail(ASRQ_ERR_NULL, "asrq_check_status: workspace is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned host[2] = {0, 0};
+  ASRQ_CUDA_TRY(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, st));
+  ASRQ_CUDA_TRY(cudaStreamSynchronize(st));
+  if (host[0] == 0) return ASRQ_OK;
+  ASRQ_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(host), st));
+  ASRQ_CUDA_TRY(cudaStreamSynchronize(st));
+  return fail(ASRQ_ERR_TIMEOUT, "a device-side wait gave up at site %u", host[1]);
+}
+
+int asrq_device_info_query(int device, asrq_device_info* out) {
+  last_error().clear();
+  if (!out) return fail(ASRQ_ERR_NULL, "asrq_device_info_query: out is NULL");
+  cudaDeviceProp prop;
+  ASRQ_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  std::memset(out, 0, sizeof(*out));
+  std::strncpy(out->name, prop.name, sizeof(out->name) - 1);
+  out->cc_major = prop.major;
+  out->cc_minor = prop.minor;
+  out->sm_count = prop.multiProcessorCount;
+  out->max_smem_per_block_optin = int(prop.sharedMemPerBlockOptin);
+  out->l2_bytes = prop.l2CacheSize;
+  int v = 0;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, device) == cudaSuccess) out->clock_khz = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, device) == cudaSuccess) out->mem_clock_khz = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrGlobalMemoryBusWidth, device) == cudaSuccess) out->mem_bus_bits = v;
+  out->total_mem = prop.totalGlobalMem;
+  return ASRQ_OK;
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,115 @@
+// Shared host/device helpers of the asrq_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/asrq_b200.h"
+
+namespace asrq {
+
+// ---- host: per-thread error text ------------------------------------------------
+std::string& last_error();
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define ASRQ_CUDA_TRY(expr)                                  \
+  do {                                                       \
+    cudaError_t e__ = (expr);                                \
+    if (e__ != cudaSuccess) return asrq::cuda_fail(e__, #expr); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- workspace layout --------------------------------------------------------------
+// [0,256)            status block: word 0 = error flag (0 ok), word 1 = where a wait gave up
+// [256, 256+16384)   4096 tile counters (zero between calls)
+// [16640, ...)       fp32 split-K partial sums
+constexpr size_t kStatusBytes = 256;
+constexpr size_t kCounterBytes = 4096 * sizeof(unsigned);
+constexpr size_t kPartialOffset = kStatusBytes + kCounterBytes;
+constexpr int kGemvMaxSplit = 32;
+
+// ---- device helpers ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(x), "r"(mask), "r"(orv));  // (x & mask) | orv
+  return r;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Convert one 32-bit word of packed weights into fp16 pairs of exact integer codes.
+// 4-bit: out[i] = (e_i, e_{i+4}), i = 0..3.   2-bit: out[i] = (e_i, e_{i+8}), i = 0..7.
+// The caller pairs them with activations stored in the same (i, i+4) / (i, i+8) order.
+template <int BITS>
+__device__ __forceinline__ void unpack_codes_f16(uint32_t q, __half2* out) {
+  const uint32_t magic = 0x64006400u;  // 1024.0 in both halves
+  if (BITS == 4) {
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));  // 1/16
+    const __half2 km64 = __half2half2(__ushort_as_half(0xd400));   // -64
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t lo = lop3_and_or(q, 0x000f000fu, magic);
+      uint32_t hi = lop3_and_or(q, 0x00f000f0u, magic);
+      out[2 * j] = __hsub2(u32_as_h2(lo), k1024);
+      out[2 * j + 1] = __hfma2(u32_as_h2(hi), k16th, km64);
+      q >>= 8;
+    }
+  } else {
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    const __half2 k4th = __half2half2(__ushort_as_half(0x3400));    // 1/4
+    const __half2 km256 = __half2half2(__ushort_as_half(0xdc00));   // -256
+    const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
+    const __half2 km64 = __half2half2(__ushort_as_half(0xd400));    // -64
+    const __half2 k64th = __half2half2(__ushort_as_half(0x2400));   // 1/64
+    const __half2 km16 = __half2half2(__ushort_as_half(0xcc00));    // -16
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t f0 = lop3_and_or(q, 0x00030003u, magic);
+      uint32_t f1 = lop3_and_or(q, 0x000c000cu, magic);
+      uint32_t f2 = lop3_and_or(q, 0x00300030u, magic);
+      uint32_t f3 = lop3_and_or(q, 0x00c000c0u, magic);
+      out[4 * j] = __hsub2(u32_as_h2(f0), k1024);
+      out[4 * j + 1] = __hfma2(u32_as_h2(f1), k4th, km256);
+      out[4 * j + 2] = __hfma2(u32_as_h2(f2), k16th, km64);
+      out[4 * j + 3] = __hfma2(u32_as_h2(f3), k64th, km16);
+      q >>= 8;
+    }
+  }
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
+
+__device__ __forceinline__ uint16_t float_to_out16(float v, bool bf16) {
+  if (bf16) {
+    __nv_bfloat16 b = __float2bfloat16_rn(v);
+    return *reinterpret_cast<uint16_t*>(&b);
+  }
+  __half h = __float2half_rn(v);
+  return *reinterpret_cast<uint16_t*>(&h);
+}
+
+}  // namespace asrq

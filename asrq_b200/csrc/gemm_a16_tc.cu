@@ -1,0 +1,345 @@
+// Prefill / encoder path: y[M,N] = x[M,K] . dequant(W)[N,K]^T (+ bias) for large M.
+//
+// The weight tile is the MMA "A" operand (128 output features = 128 TMEM lanes), the
+// activation tile is the "B" operand (BT tokens = BT TMEM columns, BT <= 256 chosen
+// by the host).  One persistent block per SM, ten warps:
+//
+//   warp 0      TMA producer: per 64-wide K block, one tile of activations
+//               (BT x 64, 128-byte swizzle) and one tile of packed weights (128 rows).
+//   warp 1      MMA issuer: tcgen05.mma kind::f16, 4 x (128 x BT x 16) per K block,
+//               fp32 accumulators in TMEM, two accumulator buffers of 256 columns.
+//   warps 2-5   dequant: one weight row per thread; packed words -> fp16/bf16 in
+//               registers -> q*scale+zero -> the swizzled K-major A tile in shared memory.
+//   warps 6-9   epilogue: tcgen05.ld of the previous tile's accumulator, + bias,
+//               convert, store, while the next tile's main loop runs.
+//
+// Rings: full[s] (TMA landed) -> deq[s] (A tile written) -> MMA -> empty[s] (MMA done,
+// stage reusable); accf[b]/acce[b] hand the accumulator buffers back and forth.
+// Every wait is bounded (tcgen05.cuh).
+#include <algorithm>
+
+#include "tcgen05.cuh"
+
+namespace asrq {
+
+struct GemmTcParams {
+  const __half* scales;
+  const __half* zeros;
+  const __half* bias;
+  uint16_t* y;
+  unsigned* status;
+  int M, N, K, group_size, groups_per_row, bt, nstages, n_ftiles, n_ttiles;
+};
+
+constexpr int kTcThreads = 320;
+constexpr int kTcMaxStages = 8;
+constexpr uint32_t kATileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
+constexpr uint32_t kWSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
+
+// One 32-bit word of packed weights -> 16-bit floats in natural k order, scaled.
+// out holds 32/BITS/2 packed pairs.
+template <int BITS, bool BF16>
+__device__ __forceinline__ void dequant_word(uint32_t q, uint32_t s2, uint32_t z2, uint32_t* out) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t t = prmt(q, q, 0x1111u * j);  // byte j replicated
+    if (!BF16) {
+      const uint32_t magic = 0x64006400u;  // 1024 | field
+      if (BITS == 4) {
+        const uint32_t v = lop3_and_or(t, 0x00f0000fu, magic);  // (1024+e0, 1024+16*e1)
+        const __half2 c = __hfma2(u32_as_h2(v), u32_as_h2(0x2c003c00u), u32_as_h2(0xd400e400u));
+        out[j] = h2_as_u32(__hfma2(c, u32_as_h2(s2), u32_as_h2(z2)));
+      } else {
+        const uint32_t v0 = lop3_and_or(t, 0x000c0003u, magic);  // (1024+e0, 1024+4*e1)
+        const uint32_t v1 = lop3_and_or(t, 0x00c00030u, magic);  // (1024+16*e2, 1024+64*e3)
+        const __half2 c0 = __hfma2(u32_as_h2(v0), u32_as_h2(0x34003c00u), u32_as_h2(0xdc00e400u));
+        const __half2 c1 = __hfma2(u32_as_h2(v1), u32_as_h2(0x24002c00u), u32_as_h2(0xcc00d400u));
+        out[2 * j] = h2_as_u32(__hfma2(c0, u32_as_h2(s2), u32_as_h2(z2)));
+        out[2 * j + 1] = h2_as_u32(__hfma2(c1, u32_as_h2(s2), u32_as_h2(z2)));
+      }
+    } else {
+      const uint32_t magic = 0x43004300u;  // 128 | field (7 mantissa bits)
+      const __nv_bfloat162 k128 = *reinterpret_cast<const __nv_bfloat162*>(&magic);
+      const __nv_bfloat162 sb = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+      const __nv_bfloat162 zb = *reinterpret_cast<const __nv_bfloat162*>(&z2);
+      if (BITS == 4) {
+        uint32_t r = lop3_and_or(t >> 4, 0x000f0000u, magic);
+        r = lop3_and_or(t, 0x0000000fu, r);
+        const __nv_bfloat162 c = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&r), k128);
+        const __nv_bfloat162 w = __hfma2(c, sb, zb);
+        out[j] = *reinterpret_cast<const uint32_t*>(&w);
+      } else {
+        uint32_t r0 = lop3_and_or(t >> 2, 0x00030000u, magic);
+        r0 = lop3_and_or(t, 0x00000003u, r0);
+        uint32_t r1 = lop3_and_or(t >> 6, 0x00030000u, magic);
+        r1 = lop3_and_or(t >> 4, 0x00000003u, r1);
+        const __nv_bfloat162 w0 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&r0), k128), sb, zb);
+        const __nv_bfloat162 w1 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&r1), k128), sb, zb);
+        out[2 * j] = *reinterpret_cast<const uint32_t*>(&w0);
+        out[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&w1);
+      }
+    }
+  }
+}
+
+template <int BITS, bool BF16>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
+                   const GemmTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[3 * kTcMaxStages + 4];
+  __shared__ uint32_t tmem_slot;
+
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t xbytes = uint32_t(p.bt) * 128u;
+  const uint32_t stage_bytes = xbytes + kATileBytes + kWSlotBytes;
+  constexpr uint32_t wbytes = 128u * 8u * BITS;
+  const int nst = p.nstages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = tc::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto deq_bar = [&](int s) { return bar0 + 8u * (kTcMaxStages + s); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (2 * kTcMaxStages + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kTcMaxStages + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kTcMaxStages + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nst; ++s) {
+      tc::mbar_init(full_bar(s), 1);
+      tc::mbar_init(deq_bar(s), 128);
+      tc::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(accf_bar(b), 1);
+      tc::mbar_init(acce_bar(b), 128);
+    }
+    tc::fence_barrier_init();
+    tc::fence_proxy_async_smem();
+    tc::prefetch_tmap(&tmx);
+    tc::prefetch_tmap(&tmw);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+
+  const int ntiles = p.n_ftiles * p.n_ttiles;
+  const int nkb = p.K / 64;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % nst;
+          const uint32_t ph = (it / nst) & 1u;
+          if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
+          const uint32_t sb = base + s * stage_bytes;
+          tc::mbar_arrive_expect_tx(full_bar(s), xbytes + wbytes);
+          tc::tma_load_2d(sb, &tmx, kb * 64, tt * p.bt, full_bar(s));
+          tc::tma_load_2d(sb + xbytes + kATileBytes, &tmw, kb * 8 * BITS, ft * 128, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = tc::instr_desc(1u, BF16 ? 1u : 0u, 128u, uint32_t(p.bt));
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
+        if (!tc::mbar_wait(acce_bar(buf), aph ^ 1u, p.status, 2)) { ok = false; break; }
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * 256u;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % nst;
+          const uint32_t ph = (it / nst) & 1u;
+          if (!tc::mbar_wait(full_bar(s), ph, p.status, 3) || !tc::mbar_wait(deq_bar(s), ph, p.status, 4)) {
+            ok = false;
+            break;
+          }
+          tc::fence_after_sync();
+          const uint32_t sb = base + s * stage_bytes;
+          const uint32_t a_addr = sb + xbytes, b_addr = sb;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc::mma_f16(d_tmem, tc::smem_desc_sw128(a_addr + 32u * k), tc::smem_desc_sw128(b_addr + 32u * k),
+                        idesc, uint32_t((kb | k) != 0));
+          tc::mma_commit(empty_bar(s));
+        }
+        if (ok) tc::mma_commit(accf_bar(buf));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------ dequant ------------------------------
+    const int t = threadIdx.x - 64;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      const int ft = tile % p.n_ftiles;
+      const size_t row = size_t(ft) * 128 + t;
+      const __half* sc = p.scales + row * p.groups_per_row;
+      const __half* zr = p.zeros + row * p.groups_per_row;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % nst;
+        const uint32_t ph = (it / nst) & 1u;
+        const int gi = (kb * 64) / p.group_size;
+        const __half sh = __ldg(sc + gi), zh = __ldg(zr + gi);
+        uint32_t s2, z2;
+        if (BF16) {
+          const __nv_bfloat162 sb2 = __float2bfloat162_rn(__half2float(sh));
+          const __nv_bfloat162 zb2 = __float2bfloat162_rn(__half2float(zh));
+          s2 = *reinterpret_cast<const uint32_t*>(&sb2);
+          z2 = *reinterpret_cast<const uint32_t*>(&zb2);
+        } else {
+          s2 = h2_as_u32(__half2half2(sh));
+          z2 = h2_as_u32(__half2half2(zh));
+        }
+        if (!tc::mbar_wait(full_bar(s), ph, p.status, 5)) { ok = false; break; }
+        uint8_t* sb = smem + s * stage_bytes;
+        const uint4* wp = reinterpret_cast<const uint4*>(sb + xbytes + kATileBytes + t * (8 * BITS));
+        uint8_t* arow = sb + xbytes + t * 128;
+        constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const uint4 qv = wp[v];
+          const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            constexpr int PW = 32 / BITS / 2;  // output pairs per word: 4 or 8
+            uint32_t o[PW];
+            dequant_word<BITS, BF16>(qw[j], s2, z2, o);
+#pragma unroll
+            for (int cc = 0; cc < PW / 4; ++cc) {
+              const int chunk = (v * 4 + j) * (PW / 4) + cc;  // 16-byte chunk (8 elements) in the row
+              *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) =
+                  make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
+            }
+          }
+        }
+        tc::fence_proxy_async_smem();
+        tc::mbar_arrive(deq_bar(s));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int qd = warp & 3;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+      const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+      const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
+      const int f = ft * 128 + qd * 32 + lane;
+      const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
+      if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
+      tc::fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
+      for (int ch = 0; ch < p.bt / 32; ++ch) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(taddr + ch * 32, r);
+        tc::tmem_ld_wait();
+        const int t0 = tt * p.bt + ch * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int tok = t0 + j;
+          if (tok < p.M) p.y[size_t(tok) * p.N + f] = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+        }
+      }
+      tc::fence_before_sync();
+      tc::mbar_arrive(acce_bar(buf));
+    }
+  }
+
+  __syncwarp();
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Token-tile width: the multiple of 32 (<= 256, <= M) that minimises
+// rounds-over-the-SMs x (tile width + fixed per-tile overhead).
+int gemm_tc_pick_bt(int64_t M, int64_t N, int sm_count) {
+  int best = 32;
+  double best_cost = 1e30;
+  const int64_t nft = N / 128;
+  for (int bt = 32; bt <= 256; bt += 32) {
+    if (bt > M && bt != 32) break;
+    const int64_t tiles = nft * ((M + bt - 1) / bt);
+    const int64_t rounds = (tiles + sm_count - 1) / sm_count;
+    const double cost = double(rounds) * (bt + 24);
+    if (cost <= best_cost) {
+      best_cost = cost;
+      best = bt;
+    }
+  }
+  return best;
+}
+
+template <int BITS, bool BF16>
+static int launch_tc(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmTcParams& p, int grid, size_t smem,
+                     cudaStream_t stream) {
+  auto kern = gemm_a16_tc_kernel<BITS, BF16>;
+  ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  kern<<<grid, kTcThreads, smem, stream>>>(tmx, tmw, p);
+  ASRQ_CUDA_TRY(cudaGetLastError());
+  return ASRQ_OK;
+}
+
+int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+  if (N % 128 || K % 64 || group_size <= 0 || group_size % 64 || K % group_size)
+    return fail(ASRQ_ERR_SHAPE,
+                "w%da16 gemm: need N%%128==0, K%%64==0, group_size%%64==0, K%%group_size==0 "
+                "(N=%lld K=%lld g=%d)", bits, (long long)N, (long long)K, group_size);
+  if (M < 32) return fail(ASRQ_ERR_SHAPE, "w%da16 gemm: M=%lld < 32 (use the gemv entry point)", bits, (long long)M);
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w%da16 gemm: size", bits);
+  if (workspace_bytes < kStatusBytes) return fail(ASRQ_ERR_WORKSPACE, "w%da16 gemm: workspace too small", bits);
+  if (!aligned16(x) || !aligned16(w)) return fail(ASRQ_ERR_ALIGN, "w%da16 gemm: x and w must be 16-byte aligned", bits);
+
+  GemmTcParams p;
+  p.scales = static_cast<const __half*>(scales);
+  p.zeros = static_cast<const __half*>(zeros);
+  p.bias = static_cast<const __half*>(bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.status = static_cast<unsigned*>(workspace);
+  p.M = int(M);
+  p.N = int(N);
+  p.K = int(K);
+  p.group_size = group_size;
+  p.groups_per_row = int(K / group_size);
+  p.bt = gemm_tc_pick_bt(M, N, sm_count);
+  p.n_ftiles = int(N / 128);
+  p.n_ttiles = int((M + p.bt - 1) / p.bt);
+  const size_t stage_bytes = size_t(p.bt) * 128 + kATileBytes + kWSlotBytes;
+  const size_t budget = 227 * 1024 - 1024 - 512;
+  p.nstages = int(std::min<size_t>(kTcMaxStages, budget / stage_bytes));
+  const size_t smem = 1024 + p.nstages * stage_bytes;
+
+  const bool bf16 = dtype == ASRQ_BF16;
+  CUtensorMap tmx, tmw;
+  int rc = make_tmap_2d(&tmx, x, 2, bf16, uint64_t(K), uint64_t(M), 64, uint32_t(p.bt), true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmw, w, 1, false, uint64_t(K) * bits / 8, uint64_t(N), uint32_t(8 * bits), 128, false);
+  if (rc) return rc;
+  const int grid = int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles, sm_count));
+  if (bits == 4)
+    return bf16 ? launch_tc<4, true>(tmx, tmw, p, grid, smem, stream) : launch_tc<4, false>(tmx, tmw, p, grid, smem, stream);
+  return bf16 ? launch_tc<2, true>(tmx, tmw, p, grid, smem, stream) : launch_tc<2, false>(tmx, tmw, p, grid, smem, stream);
+}
+
+}  // namespace asrq

@@ -1,0 +1,168 @@
+// Blackwell (sm_100a) primitives used by the tensor-core kernels: mbarrier with
+// bounded waits, TMA tile loads, TMEM allocation, tcgen05.mma / commit / ld and the
+// shared-memory and instruction descriptors they take.
+#pragma once
+
+#include <cuda.h>  // CUtensorMap (types only; the encoder is fetched at run time)
+
+#include "common.cuh"
+
+namespace asrq {
+namespace tc {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier ----------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Every wait in these kernels is bounded: after kWaitCycles SM clocks without the
+// barrier completing, the waiter records where it gave up in the status block
+// (word 0 = 1, word 1 = site) and returns false; the caller then leaves its loop
+// and the block tears down normally.  The host reads the block with
+// asrq_check_status.
+constexpr long long kWaitCycles = 400000000ll;  // ~0.2 s at 1.9 GHz
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitCycles) {
+      if (atomicCAS(status, 0u, 1u) == 0u) status[1] = site;
+      return false;
+    }
+  }
+}
+
+// ---- TMA -----------------------------------------------------------------------------
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+// 2-D tile load global -> shared, completion counted in bytes on `bar`.
+// c0 is the innermost coordinate; c0 * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+// ---- TMEM ----------------------------------------------------------------------------
+// Whole-warp operations.
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---- descriptors -----------------------------------------------------------------------
+// Shared-memory operand, K-major, 128-byte swizzle: rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart (stride byte offset), 16-byte chunk index XOR (row & 7) inside a
+// row.  The tile base must be 1024-byte aligned; a K step of 32 bytes inside the row
+// is taken by advancing the start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= uint64_t((addr & 0x3ffffu) >> 4);  // start address, 16-byte units
+  d |= uint64_t(1) << 16;                 // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t(1024 >> 4) << 32;         // stride byte offset
+  d |= uint64_t(1) << 46;                 // descriptor version (sm_100)
+  d |= uint64_t(2) << 61;                 // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor.  D format: 1 = f32, 2 = s32.  A/B format for kind::f16:
+// 0 = f16, 1 = bf16; for kind::i8: 0 = u8, 1 = s8.  Both operands K-major.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t dfmt, uint32_t abfmt, uint32_t m, uint32_t n) {
+  return (dfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- MMA (single thread) -----------------------------------------------------------------
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives once on `bar` when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+// ---- TMEM -> registers: lane = 32*(warp%4) + laneid, 32 consecutive 32-bit columns ------------
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace tc
+
+// ---- host: tensor maps ----------------------------------------------------------------------
+// 2-D row-major tensor of `rows` x `inner` elements of `elem_bytes` bytes (1 or 2),
+// box `box_inner` x `box_rows`.  swizzle128: 128-byte swizzle (box_inner*elem_bytes == 128)
+// or none.  Returns 0 or a negative ASRQ status.
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool bf16, uint64_t inner, uint64_t rows,
+                 uint32_t box_inner, uint32_t box_rows, bool swizzle128);
+
+}  // namespace asrq

@@ -1,0 +1,207 @@
+"""Drop-in ``LinearQ`` / ``LinearQQ`` modules backed by the B200 kernels.
+
+Same constructor, buffer names, shapes and dtypes, ``state_dict`` keys and
+``forward(input)`` contract as the reference module (asrq/core/linear.py:8-86), so the
+``Whisper*Q`` / ``Qwen3*Q`` / ``Conformer*Q`` classes can import it unchanged.  The
+forward pass calls the C ABI (``include/asrq_b200.h``); there is no CPU or PyTorch
+fallback -- a CPU tensor, or a missing library, raises.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_CHECK = os.environ.get("ASRQ_B200_CHECK_STATUS", "0") == "1"
+
+# one scratch buffer per (device, stream): kernels on one stream run in order, so they can share it
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises if a kernel on the current stream reported a bounded wait that gave up."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is not None:
+        _lib.call("asrq_check_status", ws.data_ptr(), key[1])
+
+
+def _as_2d(x: torch.Tensor, k: int) -> torch.Tensor:
+    if x.shape[-1] != k:
+        raise ValueError(f"last dimension of the input is {x.shape[-1]}, expected in_features={k}")
+    x2 = x.reshape(-1, k)
+    return x2 if x2.is_contiguous() else x2.contiguous()
+
+
+def _require_cuda_16bit(x: torch.Tensor, who: str) -> int:
+    if not x.is_cuda:
+        raise RuntimeError(f"{who}: input is on {x.device}; asrq_b200 runs on CUDA (sm_100a) only and has no CPU path")
+    try:
+        return _DTYPES[x.dtype]
+    except KeyError:
+        raise TypeError(f"{who}: input dtype {x.dtype} is not supported (float16 or bfloat16)") from None
+
+
+class LinearQ(nn.Module):
+    """Linear layer with packed 2-/4-bit weights and per-group fp16 scales and zeros.
+
+    Mirrors asrq/core/linear.py:8-66: ``weight`` uint8 (out, in*bits/8), ``scales`` and
+    ``zeros`` fp16 (out, ceil(in/group_size)), ``bias`` fp16 (out) or None;
+    ``W[n,k] = q[n,k]*scales[n,k//g] + zeros[n,k//g]``; ``forward`` returns
+    ``input @ W.T (+ bias)`` in the input dtype with the input's leading dimensions.
+    """
+
+    def __init__(self, in_features, out_features, bits, group_size=128, bias=True):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.group_size = group_size
+        self.bits = bits
+        self.register_buffer("weight", torch.zeros((out_features, in_features // (8 // bits)), dtype=torch.uint8))
+        if bias:
+            self.register_buffer("bias", torch.zeros(out_features, dtype=torch.float16))
+        else:
+            self.bias = None
+        ngroups = (in_features + group_size - 1) // group_size
+        self.register_buffer("scales", torch.zeros((out_features, ngroups), dtype=torch.float16))
+        self.register_buffer("zeros", torch.zeros((out_features, ngroups), dtype=torch.float16))
+
+    def load_quantized_params(self, scales, zeros, quantized_weight):
+        """Binds already-packed parameters, moving them to the module's device (linear.py:27-31)."""
+        self.scales = scales.to(self.scales.device)
+        self.zeros = zeros.to(self.zeros.device)
+        self.weight = quantized_weight.to(self.weight.device)
+
+    def dequantize_weight(self, device="cpu", dtype=torch.float32):
+        """Full (out, in) weight in ``dtype`` with the reference's two-step rounding
+        (linear.py:33-54).  A debugging aid; ``forward`` never calls it."""
+        g, k = self.group_size, self.in_features
+        scale = self.scales.repeat_interleave(g, dim=1).to(device).to(dtype)[:, :k]
+        zero = self.zeros.repeat_interleave(g, dim=1).to(device).to(dtype)[:, :k]
+        wq = self.weight.to(device)
+        q = torch.zeros((self.out_features, k), device=device, dtype=dtype)
+        if self.bits == 4:
+            q[:, 0::2] = (wq & 0x0F).to(dtype)
+            q[:, 1::2] = (wq >> 4).to(dtype)
+        elif self.bits == 2:
+            for e in range(4):
+                q[:, e::4] = ((wq >> (2 * e)) & 0x03).to(dtype)
+        else:
+            raise NotImplementedError("bits must be 2 or 4")
+        return q * scale + zero
+
+    def _check_buffers(self, x: torch.Tensor) -> None:
+        for name in ("weight", "scales", "zeros"):
+            t = getattr(self, name)
+            if t.device != x.device:
+                raise RuntimeError(f"LinearQ.{name} is on {t.device} but the input is on {x.device}")
+            if not t.is_contiguous():
+                setattr(self, name, t.contiguous())
+        if self.scales.dtype != torch.float16 or self.zeros.dtype != torch.float16:
+            raise TypeError("LinearQ.scales and LinearQ.zeros must be float16")
+        if self.weight.dtype != torch.uint8:
+            raise TypeError("LinearQ.weight must be uint8")
+        if self.bias is not None and (self.bias.dtype != torch.float16 or self.bias.device != x.device):
+            raise TypeError("LinearQ.bias must be float16 on the input's device")
+
+    def forward(self, input):
+        dt = _require_cuda_16bit(input, "LinearQ.forward")
+        if self.bits not in (2, 4):
+            raise NotImplementedError("LinearQ.forward: bits must be 2 or 4")
+        self._check_buffers(input)
+        n, k = self.out_features, self.in_features
+        x2 = _as_2d(input, k)
+        m = x2.shape[0]
+        y = torch.empty((m, n), dtype=input.dtype, device=input.device)
+        if m == 0:
+            return y.reshape(*input.shape[:-1], n)
+        ws = _workspace(input.device, _lib.workspace_bytes(_lib.WS_LINEARQ, m, n, k))
+        stream = torch.cuda.current_stream(input.device).cuda_stream
+        _lib.call("asrq_linearq_a16", self.bits, x2.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
+                  self.zeros.data_ptr(), None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
+                  m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
+        if _CHECK:
+            check_status(input.device)
+        return y.reshape(*input.shape[:-1], n)
+
+    def extra_repr(self):
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.bits}, "
+                f"group_size={self.group_size}, bias={self.bias is not None}")
+
+
+class LinearQQ(LinearQ):
+    """W4A4 linear: online Hadamard rotation + per-token int4 activations, grouped int4 weights.
+
+    Constructor signature of the reference stub (asrq/core/linear.py:69-75), whose
+    ``forward`` returns None.  ``weight`` holds two's-complement signed nibbles
+    (asrq/matmulq/test.py:141-142), ``scales`` the per-(row, group) weight scales;
+    ``zeros`` is unused and stays zero.  ``forward`` computes
+
+        v = hadU(x) (if ``hadamard``);  s = absmax(v)/7 per token;  q = rint(v/s)
+        y[m,n] = s[m] * sum_g (sum_{k in g} q[m,k]*qw[n,k]) * scales[n,g]  (+ bias[n])
+
+    which equals ``x @ W.T`` up to quantisation error when ``weight`` was produced by
+    :func:`asrq_b200.packing.pack_w4a4` with the same ``hadamard`` flag.
+    """
+
+    def __init__(self, in_features, out_features, wbits, abits, group_size=128, bias=True, hadamard=True):
+        if wbits != 4 or abits != 4:
+            raise NotImplementedError("LinearQQ supports wbits=4, abits=4")
+        super().__init__(in_features, out_features, wbits, group_size, bias)
+        self.register_buffer("act_scales", torch.ones(in_features))
+        self.amax = 2 ** (abits - 1) - 1
+        self.abits = abits
+        self.hadamard = hadamard
+
+    def _quantize(self, input):
+        dt = _require_cuda_16bit(input, "LinearQQ")
+        x2 = _as_2d(input, self.in_features)
+        m, k = x2.shape
+        qa = torch.empty((m, k // 2), dtype=torch.uint8, device=input.device)
+        sa = torch.empty((m,), dtype=torch.float32, device=input.device)
+        stream = torch.cuda.current_stream(input.device).cuda_stream
+        _lib.call("asrq_hadamard_quant_int4", x2.data_ptr(), qa.data_ptr(), sa.data_ptr(), m, k,
+                  1 if self.hadamard else 0, dt, stream)
+        return qa, sa, dt, stream
+
+    def quantize_activation(self, input):
+        """(codes, scales): integer-valued float codes (M,K) and per-token scales (M,1), the
+        return convention of the reference method (linear.py:77-82), computed by the CUDA prologue."""
+        qa, sa, _, _ = self._quantize(input)
+        p = qa.to(torch.int32)
+        lo, hi = p & 0xF, (p >> 4) & 0xF
+        lo = torch.where(lo >= 8, lo - 16, lo)
+        hi = torch.where(hi >= 8, hi - 16, hi)
+        q = torch.stack((lo, hi), dim=-1).reshape(qa.shape[0], -1).to(torch.float32)
+        return q, sa.reshape(-1, 1)
+
+    def forward(self, input, acc_dump=None):
+        self._check_buffers(input)
+        if input.numel() == 0:
+            _require_cuda_16bit(input, "LinearQQ")
+            return input.new_empty(*input.shape[:-1], self.out_features)
+        qa, sa, dt, stream = self._quantize(input)
+        m, n, k = qa.shape[0], self.out_features, self.in_features
+        y = torch.empty((m, n), dtype=input.dtype, device=input.device)
+        ws = _workspace(input.device, _lib.workspace_bytes(_lib.WS_W4A4_GEMM, m, n, k))
+        _lib.call("asrq_w4a4_gemm", qa.data_ptr(), sa.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
+                  None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
+                  None if acc_dump is None else acc_dump.data_ptr(), m, n, k, self.group_size, dt,
+                  ws.data_ptr(), ws.numel(), stream)
+        if _CHECK:
+            check_status(input.device)
+        return y.reshape(*input.shape[:-1], n)

@@ -1,0 +1,172 @@
+/*
+ * asrq_b200 -- C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * This is the native boundary behind the reference's `LinearQ` Python module
+ * (asrq/core/linear.py:8-66).  It replaces the torch-C++/pybind11 extension of
+ * the reference (asrq/matmulq/csrc/bindings.cpp:805-896, built at import by
+ * asrq/matmulq/base.py:102-110).  Conventions, chosen against the reference's:
+ *
+ *   - plain C: raw DEVICE pointers, int64 sizes, the CUDA stream as `void*`
+ *     (a cudaStream_t; the reference takes at::cuda::getCurrentCUDAStream(),
+ *     bindings.cpp:188);
+ *   - every function returns an int status: 0 = ok, negative = argument error
+ *     found on the host before any launch, positive = a cudaError_t.  Nothing
+ *     here calls exit() (the reference's CUDA_CHECK does, csrc/cuda/common.h:5-12);
+ *   - the caller owns all memory, including the scratch `workspace`
+ *     (size from asrq_workspace_bytes); no entry point allocates, frees or
+ *     synchronises, so all of them are safe on any stream;
+ *   - all matrices are row-major and contiguous.  `dtype` selects the 16-bit
+ *     activation / output format (ASRQ_F16 or ASRQ_BF16); scales, zeros and bias
+ *     are always fp16, as LinearQ registers them (linear.py:18-25).
+ *
+ * Packed weight layout (defined by LinearQ.dequantize_weight, linear.py:33-54):
+ *   4-bit: byte j of a row holds k=2j in bits[0,3] and k=2j+1 in bits[4,7];
+ *   2-bit: byte j of a row holds k=4j+e in bits[2e,2e+1];
+ *   W[n,k] = q[n,k]*scales[n,k/g] + zeros[n,k/g], q unsigned, zeros an additive
+ *   fp16 offset.  The W4A4 path instead uses two's-complement signed nibbles in
+ *   the same positions (asrq/matmulq/test.py:141-142) and scales only.
+ */
+#ifndef ASRQ_B200_H_
+#define ASRQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ASRQ_F16 0
+#define ASRQ_BF16 1
+
+/* status codes (negative: rejected on the host, nothing was launched) */
+#define ASRQ_OK 0
+#define ASRQ_ERR_NULL (-1)      /* a required pointer is NULL */
+#define ASRQ_ERR_SHAPE (-2)     /* M/N/K/group_size outside what the kernel supports */
+#define ASRQ_ERR_ALIGN (-3)     /* a pointer is not 16-byte aligned */
+#define ASRQ_ERR_WORKSPACE (-4) /* workspace missing or smaller than asrq_workspace_bytes */
+#define ASRQ_ERR_DTYPE (-5)     /* dtype is neither ASRQ_F16 nor ASRQ_BF16 */
+#define ASRQ_ERR_DEVICE (-6)    /* current device is not sm_100 */
+#define ASRQ_ERR_TIMEOUT (-7)   /* a bounded device-side wait gave up (see asrq_check_status) */
+#define ASRQ_ERR_LIMIT (-8)     /* size beyond a fixed built-in maximum */
+
+/* workspace kinds for asrq_workspace_bytes */
+#define ASRQ_WS_A16_GEMV 1
+#define ASRQ_WS_A16_GEMM 2
+#define ASRQ_WS_W4A4_GEMM 3
+#define ASRQ_WS_LINEARQ 4 /* max over everything asrq_linearq_a16 may dispatch to */
+
+/*
+ * Bytes of scratch the caller must pass as `workspace` for one call of the
+ * given kind and shape.  The first 256 bytes of every workspace are a status
+ * block that must be zero before the first use (cudaMemset once); the kernels
+ * keep it consistent afterwards.  Counterpart of mymatmul_workspace_sizes
+ * (asrq/matmulq/csrc/bindings.cpp:17-22,192-198), which sized the reference's
+ * stream-K workspace and lock array.
+ */
+size_t asrq_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
+
+/*
+ * y[M,N] = x[M,K] . dequant(w)[N,K]^T (+ bias[N]) for 4-bit / 2-bit weights, small M
+ * (the decode path): split-K skinny GEMM bound by HBM bandwidth.  Any M >= 1 is
+ * accepted (row blocks of 16 are streamed one after the other).
+ * Requires N % 16 == 0, group_size % 32 == 0 (4-bit) or % 64 == 0 (2-bit),
+ * K % 128 == 0 (4-bit) or K % 256 == 0 (2-bit), K % group_size == 0.
+ * Replaces the declared-but-sourceless matmul_f16xint4 / matmul_f16xint2 /
+ * matmul_w4a16_sym of the reference for M <= 64
+ * (asrq/matmulq/csrc/bindings.cpp:44-57, 607-650, 705-747, 773-781).
+ */
+int asrq_w4a16_gemv(const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                    const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size,
+                    int dtype, void* workspace, size_t workspace_bytes, void* stream);
+int asrq_w2a16_gemv(const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                    const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size,
+                    int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same contraction for large M (the prefill / encoder path): weights are unpacked
+ * and scaled in registers, staged to shared memory and fed to tcgen05 kind::f16
+ * MMAs with TMEM accumulators; activations arrive by TMA.
+ * Requires N % 128 == 0, K % 64 == 0, group_size % 64 == 0, K % group_size == 0.
+ * Replaces matmul_f16xint4 / matmul_f16xint2 for M > 64
+ * (asrq/matmulq/csrc/bindings.cpp:44-57, 607-650, 705-747).
+ */
+int asrq_w4a16_gemm(const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                    const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size,
+                    int dtype, void* workspace, size_t workspace_bytes, void* stream);
+int asrq_w2a16_gemm(const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                    const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size,
+                    int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * LinearQ.forward (asrq/core/linear.py:56-66) for bits in {2,4}: dispatches on M
+ * between the two kernels above, the way the reference's matmul_w4ax switches
+ * at M = 64 (asrq/matmulq/csrc/bindings.cpp:749-803).
+ */
+int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scales,
+                     const void* zeros, const void* bias, void* y, int64_t M, int64_t N,
+                     int64_t K, int group_size, int dtype, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/*
+ * W4A4 prologue: optional online Hadamard rotation over K (normalised
+ * Walsh-Hadamard, butterflies with strides 1,2,4..K/2 then /sqrt(K), in fp32:
+ * asrq/transforms/rotation/hadamard_utils.py:60-81) followed by per-token
+ * symmetric int4 quantisation  s = absmax/7 (0 -> 1e-3),  q = rint(v/s)  with
+ * IEEE fp32 division (asrq/quantizers/activation.py:26-28, asrq/core/linear.py:77-82).
+ * Writes qa[M,K/2] (signed nibbles, even k low) and sa[M] (fp32).
+ * hadamard != 0 requires K a power of two, 256 <= K <= 8192; otherwise K % 8 == 0.
+ * Replaces per_token_quant_int4 (asrq/matmulq/csrc/bindings.cpp:69-72).
+ */
+int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K,
+                             int hadamard, int dtype, void* stream);
+
+/*
+ * W4A4 GEMM with fused dequant epilogue:
+ *   acc[m,n,g] = sum_{k in group g} qa[m,k]*qw[n,k]           (exact int32)
+ *   y[m,n]     = sa[m] * sum_g float(acc[m,n,g]) * sw[n,g]  (+ bias[n])
+ * qa[M,K/2], qw[N,K/2] signed-nibble packed; sw[N,K/group_size] fp16; sa[M] fp32.
+ * If acc_dump is not NULL the int32 group sums are also written to
+ * acc_dump[M,N,K/group_size] (for exactness checks).
+ * Requires N % 128 == 0, group_size == 128 (or 64), K % group_size == 0.
+ * Replaces matmul_wxax / matmul_w4a4 / matmul_int4_rescale
+ * (asrq/matmulq/csrc/bindings.cpp:29-43, 552-605, 652-703).
+ */
+int asrq_w4a4_gemm(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw,
+                   const void* bias, void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K,
+                   int group_size, int dtype, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+/*
+ * Reads the workspace status block back (this one DOES synchronise the stream).
+ * Returns ASRQ_OK, or ASRQ_ERR_TIMEOUT when a kernel's bounded wait gave up; the
+ * block is cleared on return.  No reference counterpart (its kernels spin unbounded,
+ * asrq/matmulq/csrc/cuda/asrq.cu:17-41).
+ */
+int asrq_check_status(void* workspace, void* stream);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* asrq_last_error_string(void);
+
+typedef struct asrq_device_info {
+  char name[128];
+  int cc_major, cc_minor;
+  int sm_count;
+  int max_smem_per_block_optin;
+  int l2_bytes;
+  int clock_khz;
+  int mem_clock_khz;
+  int mem_bus_bits;
+  size_t total_mem;
+} asrq_device_info;
+
+/* Properties of `device`; counterpart of get_gpu_metrics (bindings.cpp:101-134). */
+int asrq_device_info_query(int device, asrq_device_info* out);
+
+/* Library version, e.g. 100 = 0.1.0. */
+int asrq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASRQ_B200_H_ */

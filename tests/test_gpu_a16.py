@@ -1,0 +1,164 @@
+"""W4A16 / W2A16 parity on the GPU, through the C ABI, against the CPU oracle.
+
+Bar: |y - y_fp32| <= 2e-3 * ||row||_inf of the fp32 CPU result (fp16 outputs); bf16 outputs
+additionally get half a bf16 ulp of the reference value, because rounding the output to
+bf16 alone can cost 3.9e-3 of the row maximum.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import linearq_oracle as O
+from tests.gpu_util import DEV, assert_close_rows, bf16_half_ulp, f16, make_layer, run_a16_abi
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _ref32(case, dtype=torch.float16):
+    x = case["x"].to(dtype)
+    return O.linearq_forward_fp32(x, case["weight"], case["scales"], case["zeros"], case["bias"], case["bits"],
+                                  case["group_size"])
+
+
+def _golden_cases():
+    out = []
+    for p in sorted(glob.glob(os.path.join(GOLDEN, "linearq_*.npz"))):
+        d = np.load(p)
+        bits, g, k, n = int(d["bits"]), int(d["group_size"]), int(d["in_features"]), int(d["out_features"])
+        chunk = 128 if bits == 4 else 256
+        if k % chunk or n % 16 or g % (128 // bits):
+            continue
+        out.append(os.path.basename(p))
+    return out
+
+
+@pytest.mark.parametrize("name", _golden_cases())
+def test_golden_fixture_through_module(name):
+    """The reference's own outputs (fixtures): our fp16 output vs the reference fp32 forward."""
+    d = np.load(os.path.join(GOLDEN, name))
+    case = dict(x=f16(d["x"]), weight=torch.from_numpy(d["weight"]), scales=f16(d["scales"]), zeros=f16(d["zeros"]),
+                bias=f16(d["bias"]) if "bias" in d else None, bits=int(d["bits"]), group_size=int(d["group_size"]))
+    lq = make_layer(case)
+    y = lq(case["x"].to(DEV))
+    assert y.dtype == torch.float16 and y.shape == (case["x"].shape[0], case["weight"].shape[0])
+    assert_close_rows(y, torch.from_numpy(d["y_f32"]), what=name)
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 9, 16])
+@pytest.mark.parametrize("kn", [(2048, 6144), (6144, 2048), (2048, 4096)])
+def test_decode_shapes_gemv(bits, m, kn):
+    k, n = kn
+    case = O.make_c3(seed=1000 + m, m=m, k=k, n=n, bits=bits, group_size=64)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemv", case)
+    assert_close_rows(y, _ref32(case), what=f"gemv w{bits} m{m} {k}x{n}")
+
+
+@pytest.mark.parametrize("bits,g,m,k,n,bias", [
+    (4, 128, 5, 1280, 5120, True),    # Whisper fc1, K not a power of two
+    (4, 128, 7, 5120, 1280, True),    # Whisper fc2: K > 2048 forces a K split
+    (2, 128, 16, 1280, 1280, False),
+    (4, 32, 3, 256, 48, True),        # N not a multiple of the block's 128 rows; smallest group
+    (2, 64, 1, 256, 16, False),       # one warp strip
+    (4, 128, 17, 1024, 256, True),    # M > 16: two row blocks
+    (2, 64, 40, 512, 128, True),      # M > 32 through the skinny entry point
+])
+def test_gemv_edge_shapes(bits, g, m, k, n, bias):
+    gen = torch.Generator().manual_seed(bits * 1000 + m)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen).half(), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half() if bias else None,
+                bits=bits, group_size=g)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemv", case)
+    assert_close_rows(y, _ref32(case), what=f"gemv edge w{bits} g{g} m{m} {k}x{n}")
+
+
+def test_gemv_deterministic_and_workspace_clean():
+    """Split-K partial sums are added in slice order: repeated runs are bit-identical."""
+    case = O.make_c3(seed=7, m=4, k=6144, n=2048, bits=4, group_size=64)
+    lq = make_layer(case)
+    x = case["x"].to(DEV)
+    ys = [lq(x).clone() for _ in range(3)]
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[1], ys[2])
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_gemv_bf16(bits):
+    case = O.make_c3(seed=11, m=4, k=2048, n=4096, bits=bits, group_size=64, dtype=torch.bfloat16)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemv", case, dtype=torch.bfloat16)
+    ref = _ref32(case, torch.bfloat16)
+    assert_close_rows(y, ref, extra=bf16_half_ulp(ref), what=f"gemv bf16 w{bits}")
+
+
+def test_config1_w4a16_prefill():
+    """BASELINE config 1: K=1280 N=5120 M=1500, RTN g128 asymmetric, outliers, bias."""
+    case = O.make_c1(seed=0)
+    y = run_a16_abi("asrq_w4a16_gemm", case)
+    assert_close_rows(y, _ref32(case), what="config 1")
+
+
+@pytest.mark.parametrize("bits,g,m,k,n,bias", [
+    (4, 128, 32, 256, 128, False),     # one tile, smallest M
+    (4, 64, 33, 64, 128, True),        # one K block, ragged M
+    (4, 128, 200, 1280, 1280, True),   # Whisper attention projection
+    (2, 128, 256, 1280, 5120, True),
+    (2, 64, 1500, 2048, 256, False),
+    (4, 64, 777, 6144, 2048, False),   # long K: many ring wraps
+    (4, 128, 6000, 1024, 4096, True),  # many tiles per block: accumulator double-buffering
+])
+def test_gemm_tc_shapes(bits, g, m, k, n, bias):
+    gen = torch.Generator().manual_seed(bits * 7 + m)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen).half(), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half() if bias else None,
+                bits=bits, group_size=g)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemm", case)
+    assert_close_rows(y, _ref32(case), what=f"gemm w{bits} g{g} m{m} {k}x{n}")
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_gemm_tc_bf16(bits):
+    gen = torch.Generator().manual_seed(bits)
+    m, k, n, g = 300, 1024, 512, 128
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=None, bits=bits, group_size=g)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemm", case, dtype=torch.bfloat16)
+    ref = _ref32(case, torch.bfloat16)
+    # weights are also rounded to bf16 before the MMA: allow their rounding (2^-9 relative per weight)
+    assert_close_rows(y, ref, rel=4e-3, extra=bf16_half_ulp(ref), what=f"gemm bf16 w{bits}")
+
+
+def test_gemm_matches_gemv_and_linearity():
+    """Size-independent properties: both kernels agree, and the layer is linear in x."""
+    case = O.make_c3(seed=3, m=64, k=2048, n=1024, bits=4, group_size=64)
+    y_tc = run_a16_abi("asrq_w4a16_gemm", case).float()
+    y_gv = run_a16_abi("asrq_w4a16_gemv", case).float()
+    scale = y_gv.abs().max(dim=-1, keepdim=True).values
+    assert float(((y_tc - y_gv).abs() / scale).max()) < 2e-3
+    lq = make_layer(case)
+    x = case["x"].to(DEV)
+    y2 = lq(2 * x).float()
+    assert float(((y2 - 2 * lq(x).float()).abs() / scale.to(DEV)).max()) < 2e-3
+
+
+def test_module_dispatch_and_leading_dims():
+    case = O.make_c1(seed=1, m=96, k=1280, n=1280)
+    lq = make_layer(case)
+    x = case["x"].to(DEV).reshape(2, 3, 16, 1280)
+    y = lq(x)
+    assert y.shape == (2, 3, 16, 1280)
+    assert_close_rows(y.reshape(96, 1280), _ref32(case), what="module 4-D input")
+    y1 = lq(x[0, 0, :1])
+    assert_close_rows(y1, _ref32(case)[:1], what="module M=1")
+    empty = lq(x[:0])
+    assert empty.shape == (0, 3, 16, 1280)
+    with pytest.raises(TypeError):
+        lq(x.float())

@@ -1,0 +1,130 @@
+"""W4A4 parity on the GPU through the C ABI.
+
+Bit-exact: packed activation codes, per-token scales, int32 group accumulators.
+Within 2e-3 * ||row||_inf of the fp32 CPU composite: the fp16 output.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import asrq_b200
+from asrq_b200 import _lib
+from oracle import linearq_oracle as O
+from tests.gpu_util import DEV, assert_close_rows
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _quant_gpu(x, hadamard, dtype=torch.float16):
+    xd = x.to(dtype).to(DEV).contiguous()
+    m, k = xd.shape
+    qa = torch.empty(m, k // 2, dtype=torch.uint8, device=DEV)
+    sa = torch.empty(m, dtype=torch.float32, device=DEV)
+    _lib.call("asrq_hadamard_quant_int4", xd.data_ptr(), qa.data_ptr(), sa.data_ptr(), m, k, int(hadamard),
+              _lib.F16 if dtype == torch.float16 else _lib.BF16, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return qa.cpu(), sa.cpu()
+
+
+@pytest.mark.parametrize("k", [256, 512, 1024, 2048, 4096])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_hadamard_quant_bit_exact(k, dtype):
+    gen = torch.Generator().manual_seed(k)
+    x = torch.randn(37, k, generator=gen)
+    x[:, 3] *= 20
+    x[5] = 0.0                       # all-zero token -> scale 1e-3, codes 0
+    x[6] = 65504.0 if dtype == torch.float16 else 1e30
+    x = x.to(dtype)
+    qa, sa = _quant_gpu(x, True, dtype)
+    q_ref, s_ref, p_ref = O.hadamard_quant_int4(x, True)
+    assert torch.equal(sa, s_ref), "per-token scales differ"
+    assert torch.equal(qa, p_ref), "packed activation codes differ"
+    assert float(sa[5]) == pytest.approx(1e-3) and int(qa[5].max()) == 0
+
+
+@pytest.mark.parametrize("k", [8, 264, 1280, 5120])
+def test_quant_without_rotation_bit_exact(k):
+    gen = torch.Generator().manual_seed(k)
+    x = (torch.randn(19, k, generator=gen) * 3).half()
+    x[2] = 0.0
+    qa, sa = _quant_gpu(x, False)
+    q_ref, s_ref, p_ref = O.hadamard_quant_int4(x, False)
+    assert torch.equal(sa, s_ref) and torch.equal(qa, p_ref)
+
+
+def test_quant_matches_reference_fixture():
+    """activation.py:26-28 evaluated by the reference itself (fp32 input fixture, fed as fp16-exact values)."""
+    d = np.load(os.path.join(GOLDEN, "actquant_4bit.npz"))
+    x = torch.from_numpy(d["x"]).reshape(-1, 256).half()   # fixture values rounded to fp16 ...
+    qa, sa = _quant_gpu(x, False)
+    q, s = O.act_quant_sym(x.float(), 4)                   # ... and the pinned formula on the same values
+    assert torch.equal(O.unpack_signed_int4(qa), q) and torch.equal(sa, s.reshape(-1))
+
+
+def test_hadamard_rejects_bad_k():
+    x = torch.zeros(4, 768, dtype=torch.float16, device=DEV)
+    qa = torch.empty(4, 384, dtype=torch.uint8, device=DEV)
+    sa = torch.empty(4, dtype=torch.float32, device=DEV)
+    with pytest.raises(_lib.AsrqError) as e:
+        _lib.call("asrq_hadamard_quant_int4", x.data_ptr(), qa.data_ptr(), sa.data_ptr(), 4, 768, 1, 0, None)
+    assert e.value.code == -2
+
+
+def _w4a4_case(m, k, n, g, seed, bias=True, outliers=True):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=gen)
+    if outliers:
+        x[:, torch.randperm(k, generator=gen)[:8]] *= 20
+    x = x.half()
+    w = torch.randn(n, k, generator=gen) * 0.02
+    b = (torch.randn(n, generator=gen) * 0.02).half() if bias else None
+    return x, w, b
+
+
+@pytest.mark.parametrize("m,k,n,g,bias", [
+    (1, 256, 128, 128, False),
+    (64, 1024, 128, 128, True),
+    (100, 512, 256, 128, True),      # ragged M
+    (333, 4096, 1024, 128, True),    # config-2 widths
+    (257, 2048, 384, 128, False),
+    (48, 1024, 64, 256, True),       # wider group, narrow N: register-tile kernel
+])
+def test_w4a4_gemm_exact_accumulators_and_output(m, k, n, g, bias):
+    x, w, b = _w4a4_case(m, k, n, g, seed=m + k)
+    had = (k & (k - 1)) == 0
+    qa_ref, sa_ref, pa_ref = O.hadamard_quant_int4(x, had)
+    codes, sw, pw = O.prepare_w4a4_weight(w, g, had)
+    acc_ref = O.int4_group_accumulators(qa_ref, codes, g)
+    y_ref = O.w4a4_forward_fp32(qa_ref, sa_ref, codes, sw, b, g)
+
+    lq = asrq_b200.LinearQQ(k, n, 4, 4, g, bias=bias, hadamard=had).to(DEV)
+    pw2, sw2 = asrq_b200.pack_w4a4(w, g, had)
+    assert torch.equal(pw2, pw) and torch.equal(sw2, sw)
+    lq.load_quantized_params(sw2, torch.zeros_like(sw2), pw2)
+    if bias:
+        lq.bias = b.to(DEV)
+    acc = torch.full((m, n, k // g), -12345, dtype=torch.int32, device=DEV)
+    y = lq(x.to(DEV), acc_dump=acc)
+    asrq_b200.check_status()
+    assert torch.equal(acc.cpu(), acc_ref), "int32 group accumulators differ"
+    assert_close_rows(y, y_ref, what=f"w4a4 m{m} k{k} n{n}")
+    # and without the dump
+    y2 = lq(x.to(DEV))
+    assert torch.equal(y2, y)
+    qf, sf = lq.quantize_activation(x.to(DEV))
+    assert torch.equal(qf.cpu(), qa_ref.float()) and torch.equal(sf.cpu().reshape(-1), sa_ref)
+
+
+def test_w4a4_tracks_unquantised_product():
+    """End-to-end sanity at config-2 widths: the rotation cancels and 4x4-bit error stays moderate."""
+    x, w, b = _w4a4_case(128, 4096, 1024, 128, seed=9, bias=False)
+    lq = asrq_b200.LinearQQ(4096, 1024, 4, 4, 128, bias=False).to(DEV)
+    pw, sw = asrq_b200.pack_w4a4(w, 128, True)
+    lq.load_quantized_params(sw, torch.zeros_like(sw), pw)
+    y = lq(x.to(DEV)).float().cpu()
+    y_true = x.float() @ w.t()
+    rel = float((y - y_true).norm() / y_true.norm())
+    assert rel < 0.25, rel
