@@ -27,6 +27,7 @@ int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const vo
                  int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
                  size_t workspace_bytes, int sm_count, cudaStream_t stream);
 bool w4a4_gemm_tc_supports(int64_t M, int64_t N, int64_t K, int group_size);
+size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 // ---- errors -----------------------------------------------------------------------------
 std::string& last_error() {
@@ -142,15 +143,14 @@ int asrq_version(void) { return 100; }
 const char* asrq_last_error_string(void) { return last_error().c_str(); }
 
 size_t asrq_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
-  (void)M;
-  (void)K;
   switch (kind) {
     case ASRQ_WS_A16_GEMV:
     case ASRQ_WS_LINEARQ:
       return gemv_workspace_bytes(N);
     case ASRQ_WS_A16_GEMM:
-    case ASRQ_WS_W4A4_GEMM:
       return kStatusBytes;
+    case ASRQ_WS_W4A4_GEMM:
+      return w4a4_tc_workspace_bytes(M, N, K);
     default:
       return 0;
   }

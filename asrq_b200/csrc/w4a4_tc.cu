@@ -1,13 +1,309 @@
-// W4A4 GEMM on tcgen05 kind::i8 (int32 accumulators in TMEM).
+// W4A4 GEMM on tcgen05 kind::i8: exact int32 group sums in TMEM, fused dequant.
+//
+// Two steps per call, both on the caller's stream:
+//
+//  1. expand: packed signed nibbles -> int8 holding 16x the value (E = (q << 4) & 0xf0..,
+//     O = q & 0xf0..; the k order inside each 8-k word pair is (even k, odd k) for both
+//     operands, which a contraction does not care about).  Weights N x K and activations
+//     M x K go to the caller's workspace.  A product is 256x the true one; the factor is
+//     folded into the weight scale (an exact power of two).
+//
+//  2. GEMM: one persistent block per SM.  Weight tile = MMA A operand (128 features = TMEM
+//     lanes), activation tile = B operand (BT tokens = TMEM columns), both int8 K-major with
+//     128-byte swizzle, loaded by TMA; a K block is 128 = one row of 128 bytes = 4 MMAs of
+//     K = 32.  Every weight group (group_size / 128 K blocks) gets a fresh int32 accumulator
+//     buffer in TMEM (two buffers, ping-pong); eight drain warps read it back, convert and
+//     add float(acc) * sW[feature, group] into fp32 registers while the next group is
+//     multiplied.  After the last group: * sA[token] + bias, convert, store.
+//
+//   warp 0      TMA producer        warp 1      MMA issuer (and TMEM owner)
+//   warps 2-9   drain + epilogue: warp w reads TMEM lanes 32*(w%4).., columns half (w-2)/4.
+#include <algorithm>
+
 #include "tcgen05.cuh"
 
 namespace asrq {
 
-bool w4a4_gemm_tc_supports(int64_t, int64_t, int64_t, int) { return false; }
+__global__ void __launch_bounds__(256)
+expand_int4_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n_vec) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+    const uint4 q = __ldg(src + i);
+    uint4 lo, hi;
+    lo.x = (q.x << 4) & 0xf0f0f0f0u; lo.y = q.x & 0xf0f0f0f0u;
+    lo.z = (q.y << 4) & 0xf0f0f0f0u; lo.w = q.y & 0xf0f0f0f0u;
+    hi.x = (q.z << 4) & 0xf0f0f0f0u; hi.y = q.z & 0xf0f0f0f0u;
+    hi.z = (q.w << 4) & 0xf0f0f0f0u; hi.w = q.w & 0xf0f0f0f0u;
+    dst[2 * i] = lo;
+    dst[2 * i + 1] = hi;
+  }
+}
 
-int w4a4_gemm_tc(const uint8_t*, const float*, const uint8_t*, const void*, const void*, void*, int32_t*, int64_t,
-                 int64_t, int64_t, int, int, void*, size_t, int, cudaStream_t) {
-  return fail(ASRQ_ERR_SHAPE, "w4a4 tcgen05 gemm: shape not supported");
+struct W4A4TcParams {
+  const float* sa;
+  const __half* sw;
+  const __half* bias;
+  uint16_t* y;
+  int32_t* acc_dump;
+  unsigned* status;
+  int M, N, K, groups, blocks_per_group, bt, nstages, n_ftiles, n_ttiles, bf16;
+};
+
+constexpr int kW4A4Threads = 320;
+constexpr int kW4A4MaxStages = 8;
+constexpr uint32_t kW8TileBytes = 128 * 128;
+
+template <bool DUMP>
+__global__ void __launch_bounds__(kW4A4Threads, 1)
+w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tma,
+               const W4A4TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kW4A4MaxStages + 4];
+  __shared__ uint32_t tmem_slot;
+
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  const uint32_t bbytes = uint32_t(p.bt) * 128u;
+  const uint32_t stage_bytes = kW8TileBytes + bbytes;
+  const int nst = p.nstages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = tc::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kW4A4MaxStages + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nst; ++s) {
+      tc::mbar_init(full_bar(s), 1);
+      tc::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(accf_bar(b), 1);
+      tc::mbar_init(acce_bar(b), 256);
+    }
+    tc::fence_barrier_init();
+    tc::fence_proxy_async_smem();
+    tc::prefetch_tmap(&tmw);
+    tc::prefetch_tmap(&tma);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+
+  const int ntiles = p.n_ftiles * p.n_ttiles;
+  const int nkb = p.K / 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % nst;
+          const uint32_t ph = (it / nst) & 1u;
+          if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11)) { ok = false; break; }
+          const uint32_t sb = base + s * stage_bytes;
+          tc::mbar_arrive_expect_tx(full_bar(s), kW8TileBytes + bbytes);
+          tc::tma_load_2d(sb, &tmw, kb * 128, ft * 128, full_bar(s));
+          tc::tma_load_2d(sb + kW8TileBytes, &tma, kb * 128, tt * p.bt, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = tc::instr_desc(2u, 1u, 128u, uint32_t(p.bt));
+      uint32_t it = 0, ac = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int gb = kb % p.blocks_per_group;
+          const uint32_t buf = ac & 1u, aph = (ac >> 1) & 1u;
+          if (gb == 0) {
+            if (!tc::mbar_wait(acce_bar(buf), aph ^ 1u, p.status, 12)) { ok = false; break; }
+            tc::fence_after_sync();
+          }
+          const int s = it % nst;
+          const uint32_t ph = (it / nst) & 1u;
+          if (!tc::mbar_wait(full_bar(s), ph, p.status, 13)) { ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t sb = base + s * stage_bytes;
+          const uint32_t d_tmem = tmem_base + buf * 256u;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc::mma_i8(d_tmem, tc::smem_desc_sw128(sb + 32u * k), tc::smem_desc_sw128(sb + kW8TileBytes + 32u * k),
+                       idesc, uint32_t((gb | k) != 0));
+          tc::mma_commit(empty_bar(s));
+          if (gb == p.blocks_per_group - 1) {
+            tc::mma_commit(accf_bar(buf));
+            ++ac;
+          }
+        }
+      }
+    }
+  } else {
+    const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int hcols = p.bt >> 1;     // columns this warp drains (multiple of 32)
+    const int nch = hcols >> 5;      // 32-column chunks: 1..4
+    uint32_t ac = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+      const int f = ft * 128 + qd * 32 + lane;
+      const __half* swrow = p.sw + size_t(f) * p.groups;
+      float accf[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) accf[i] = 0.f;
+      const int tok0 = tt * p.bt + half * hcols;
+      for (int gi = 0; gi < p.groups && ok; ++gi, ++ac) {
+        const uint32_t buf = ac & 1u, aph = (ac >> 1) & 1u;
+        const float s = __half2float(__ldg(swrow + gi)) * (1.0f / 256.0f);
+        if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 14)) { ok = false; break; }
+        tc::fence_after_sync();
+        const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u + uint32_t(half * hcols);
+        if (!DUMP) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            if (ch < nch) {
+              uint32_t r[32];
+              tc::tmem_ld_32x32(taddr + ch * 32, r);
+              tc::tmem_ld_wait();
+              if (ch == nch - 1) {  // buffer fully read: hand it back before the math
+                tc::fence_before_sync();
+                tc::mbar_arrive(acce_bar(buf));
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) accf[ch * 32 + j] = fmaf(__int2float_rn(int(r[j])), s, accf[ch * 32 + j]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            if (ch < nch) {
+              uint32_t r[32];
+              tc::tmem_ld_32x32(taddr + ch * 32, r);
+              tc::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                accf[ch * 32 + j] = fmaf(__int2float_rn(int(r[j])), s, accf[ch * 32 + j]);
+                const int tok = tok0 + ch * 32 + j;
+                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = int(r[j]) >> 8;
+              }
+            }
+          }
+          tc::fence_before_sync();
+          tc::mbar_arrive(acce_bar(buf));
+        }
+      }
+      if (!ok) break;
+      const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        if (ch < nch) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = tok0 + ch * 32 + j;
+            if (tok < p.M)
+              p.y[size_t(tok) * p.N + f] = float_to_out16(accf[ch * 32 + j] * __ldg(p.sa + tok) + bias, p.bf16);
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static int w4a4_pick_bt(int64_t M, int64_t N, int sm_count) {
+  int best = 64;
+  double best_cost = 1e30;
+  const int64_t nft = N / 128;
+  for (int bt = 64; bt <= 256; bt += 64) {
+    const int64_t tiles = nft * ((M + bt - 1) / bt);
+    const int64_t rounds = (tiles + sm_count - 1) / sm_count;
+    const double cost = double(rounds) * (bt + 16);
+    if (cost <= best_cost) {
+      best_cost = cost;
+      best = bt;
+    }
+  }
+  return best;
+}
+
+bool w4a4_gemm_tc_supports(int64_t M, int64_t N, int64_t K, int group_size) {
+  return M >= 64 && N % 128 == 0 && K % 128 == 0 && group_size > 0 && group_size % 128 == 0 && K % group_size == 0 &&
+         group_size <= 4096;
+}
+
+size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  return kStatusBytes + 768 + size_t(N) * K + size_t(M) * K;
+}
+
+int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias, void* y,
+                 int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+  if (workspace_bytes < w4a4_tc_workspace_bytes(M, N, K))
+    return fail(ASRQ_ERR_WORKSPACE, "w4a4 gemm: workspace %zu < %zu bytes", workspace_bytes,
+                w4a4_tc_workspace_bytes(M, N, K));
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w4a4 gemm: size");
+  uint8_t* w8 = static_cast<uint8_t*>(workspace) + 1024;
+  uint8_t* a8 = w8 + size_t(N) * K;
+  const size_t nvec_w = size_t(N) * K / 32, nvec_a = size_t(M) * K / 32;
+  const int eb = sm_count * 8;
+  expand_int4_kernel<<<int(std::min<size_t>(eb, (nvec_w + 255) / 256)), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(qw), reinterpret_cast<uint4*>(w8), nvec_w);
+  expand_int4_kernel<<<int(std::min<size_t>(eb, (nvec_a + 255) / 256)), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(qa), reinterpret_cast<uint4*>(a8), nvec_a);
+  ASRQ_CUDA_TRY(cudaGetLastError());
+
+  W4A4TcParams p;
+  p.sa = sa;
+  p.sw = static_cast<const __half*>(sw);
+  p.bias = static_cast<const __half*>(bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.acc_dump = acc_dump;
+  p.status = static_cast<unsigned*>(workspace);
+  p.M = int(M);
+  p.N = int(N);
+  p.K = int(K);
+  p.groups = int(K / group_size);
+  p.blocks_per_group = group_size / 128;
+  p.bt = w4a4_pick_bt(M, N, sm_count);
+  p.n_ftiles = int(N / 128);
+  p.n_ttiles = int((M + p.bt - 1) / p.bt);
+  p.bf16 = dtype == ASRQ_BF16;
+  const size_t stage_bytes = kW8TileBytes + size_t(p.bt) * 128;
+  const size_t budget = 227 * 1024 - 1024 - 512;
+  p.nstages = int(std::min<size_t>(kW4A4MaxStages, budget / stage_bytes));
+  const size_t smem = 1024 + p.nstages * stage_bytes;
+
+  CUtensorMap tmw, tma;
+  int rc = make_tmap_2d(&tmw, w8, 1, false, uint64_t(K), uint64_t(N), 128, 128, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tma, a8, 1, false, uint64_t(K), uint64_t(M), 128, uint32_t(p.bt), true);
+  if (rc) return rc;
+  const int grid = int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles, sm_count));
+  if (acc_dump) {
+    ASRQ_CUDA_TRY(cudaFuncSetAttribute(w4a4_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    w4a4_tc_kernel<true><<<grid, kW4A4Threads, smem, stream>>>(tmw, tma, p);
+  } else {
+    ASRQ_CUDA_TRY(cudaFuncSetAttribute(w4a4_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    w4a4_tc_kernel<false><<<grid, kW4A4Threads, smem, stream>>>(tmw, tma, p);
+  }
+  ASRQ_CUDA_TRY(cudaGetLastError());
+  return ASRQ_OK;
 }
 
 }  // namespace asrq

@@ -143,7 +143,8 @@ class W4A4Config2(Workload):
         self.qa = torch.empty(self.M, self.K // 2, dtype=torch.uint8, device=device)
         self.sa = torch.empty(self.M, dtype=torch.float32, device=device)
         self.y = torch.empty(self.M, self.N, dtype=torch.float16, device=device)
-        self.ws = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
+        self.ws = torch.zeros(_lib.workspace_bytes(_lib.WS_W4A4_GEMM, self.M, self.N, self.K), dtype=torch.uint8,
+                              device=device)
         self.l2_note = f"rotating {nsets} input sets ({nsets * x.numel() * 2 >> 20} MiB > 126 MiB L2)"
         self.x_host = [t.cpu().pin_memory() for t in self.xs[:2]]
         self.y_host = torch.empty(self.M, self.N, dtype=torch.float16).pin_memory()
@@ -505,7 +506,6 @@ def main():
             e2e = {"value": wl.units_per_step() * world / (e2e_ms * 1e-3) / scale, "unit": wl.unit,
                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                    "api": f"asrq_b200.{type(wl.layer).__name__}.forward on a pinned host tensor, result copied to pinned host memory"}
-        from asrq_b200.linear import check_status
         _lib.call("asrq_check_status", wl.ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
         return wl, total_ms / steps, kernel_ms, clocks, e2e
 
