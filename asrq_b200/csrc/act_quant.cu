@@ -21,18 +21,29 @@ __device__ __forceinline__ float in16_to_float(uint16_t b, bool bf16) {
   return bf16 ? bf16_bits_to_float(b) : __half2float(__ushort_as_half(b));
 }
 
+__device__ __forceinline__ int quant1(float v, float s) {
+  float q = rintf(__fdiv_rn(v, s));
+  q = fminf(fmaxf(q, -7.f), 7.f);
+  return int(q);
+}
+
 __device__ __forceinline__ uint32_t pack8_int4(const float* v, float s) {
   uint32_t w = 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float q = rintf(__fdiv_rn(v[i], s));
-    q = fminf(fmaxf(q, -7.f), 7.f);
-    w |= (uint32_t(int(q)) & 0xFu) << (4 * i);
-  }
+  for (int i = 0; i < 8; ++i) w |= (uint32_t(quant1(v[i], s)) & 0xFu) << (4 * i);
   return w;
 }
 
-template <int V>
+// Four codes as int8 bytes holding 16x the value (the operand format of the tcgen05 W4A4 GEMM).
+__device__ __forceinline__ uint32_t pack4_int8x16(const float* v, float s) {
+  uint32_t w = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w |= ((uint32_t(quant1(v[i], s)) << 4) & 0xFFu) << (8 * i);
+  return w;
+}
+
+// OUT = 0: packed nibbles (K/2 bytes per token); OUT = 1: int8 holding 16*q (K bytes per token).
+template <int V, int OUT>
 __global__ void __launch_bounds__(kQuantWarps * 32)
 hadamard_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa,
                       float* __restrict__ sa, int M, int K, int bf16) {
@@ -85,6 +96,19 @@ hadamard_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa,
   float s = __fdiv_rn(amax, 7.f);
   if (s == 0.f) s = 1e-3f;
   if (lane == 0) sa[token] = s;
+  if (OUT == 1) {
+    uint32_t* d8 = reinterpret_cast<uint32_t*>(qa + size_t(token) * K + lane * V);
+    if (V >= 16) {
+#pragma unroll
+      for (int i = 0; i < V / 16; ++i)
+        reinterpret_cast<uint4*>(d8)[i] = make_uint4(pack4_int8x16(v + 16 * i, s), pack4_int8x16(v + 16 * i + 4, s),
+                                                     pack4_int8x16(v + 16 * i + 8, s), pack4_int8x16(v + 16 * i + 12, s));
+    } else {
+#pragma unroll
+      for (int i = 0; i < V / 4; ++i) d8[i] = pack4_int8x16(v + 4 * i, s);
+    }
+    return;
+  }
   uint32_t* dst = reinterpret_cast<uint32_t*>(qa + size_t(token) * (K / 2) + lane * (V / 2));
   if (V >= 32) {
 #pragma unroll
@@ -104,6 +128,7 @@ hadamard_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa,
 
 // No rotation: any K that is a multiple of 8.  Two passes over the token (the second
 // one hits L1/L2).
+template <int OUT>
 __global__ void __launch_bounds__(kQuantWarps * 32)
 quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, float* __restrict__ sa,
                   int M, int K, int bf16) {
@@ -127,7 +152,7 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
   float s = __fdiv_rn(amax, 7.f);
   if (s == 0.f) s = 1e-3f;
   if (lane == 0) sa[token] = s;
-  uint32_t* dst = reinterpret_cast<uint32_t*>(qa + size_t(token) * (K / 2));
+  uint32_t* dst = reinterpret_cast<uint32_t*>(qa + size_t(token) * (OUT == 1 ? K : K / 2));
   for (int i = lane; i < units; i += 32) {
     const uint4 u = __ldg(src + i);
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -137,26 +162,128 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
       v[2 * j] = in16_to_float(uint16_t(w[j] & 0xffffu), bf16);
       v[2 * j + 1] = in16_to_float(uint16_t(w[j] >> 16), bf16);
     }
-    dst[i] = pack8_int4(v, s);
+    if (OUT == 1) {
+      reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack4_int8x16(v, s), pack4_int8x16(v + 4, s));
+    } else {
+      dst[i] = pack8_int4(v, s);
+    }
   }
 }
 
-int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard,
-                        int dtype, cudaStream_t stream) {
-  if (M <= 0) return ASRQ_OK;
-  const uint16_t* xp = static_cast<const uint16_t*>(x);
+// K = 4096 specialisation.  The five butterfly strides that cross lanes in the generic kernel
+// (640 shuffles per lane) are replaced by one transpose through shared memory:
+//   phase A  lane L holds elements L*128 .. L*128+127 (index bits 0-6 in registers): strides 1..64;
+//   phase B  lane L holds elements o*128 + L*4 + c, o = 0..31, c = 0..3 (bits 0-1 and 7-11 in
+//            registers): strides 128..2048; the four consecutive elements pack into one store.
+// Global loads are fully coalesced and reach the phase-A layout through the same shared buffer.
+// Both exchanges use XOR-swizzled 16-byte slots and are bank-conflict free.
+template <int OUT>
+__global__ void __launch_bounds__(kQuantWarps * 32)
+hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, float* __restrict__ sa,
+                          int M, int bf16) {
+  extern __shared__ uint4 smem4[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x * kQuantWarps + warp;
+  if (token >= M) return;  // warp-uniform; only warp-level synchronisation below
+  uint4* ws = smem4 + warp * 1024;  // 16 KB per warp
+  const uint4* src = reinterpret_cast<const uint4*>(x + size_t(token) * 4096);
+#pragma unroll
+  for (int jj = 0; jj < 16; ++jj) {
+    const int u = jj * 32 + lane;  // 16-byte unit = 8 elements
+    const int owner = u >> 4, j = u & 15;
+    ws[owner * 16 + (j ^ (owner & 15))] = __ldg(src + u);
+  }
+  __syncwarp();
+  float v[128];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint4 u = ws[lane * 16 + (j ^ (lane & 15))];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[8 * j + 2 * e] = in16_to_float(uint16_t(w[e] & 0xffffu), bf16);
+      v[8 * j + 2 * e + 1] = in16_to_float(uint16_t(w[e] >> 16), bf16);
+    }
+  }
+#pragma unroll
+  for (int h = 1; h < 128; h <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 128; ++j) {
+      if ((j & h) == 0) {
+        const float a = v[j], b = v[j + h];
+        v[j] = a + b;
+        v[j + h] = a - b;
+      }
+    }
+  }
+  __syncwarp();
+  float4* wf = reinterpret_cast<float4*>(ws);
+#pragma unroll
+  for (int t = 0; t < 32; ++t) wf[lane * 32 + (t ^ lane)] = make_float4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int o = 0; o < 32; ++o) {
+    const float4 f = wf[o * 32 + (lane ^ o)];
+    v[4 * o] = f.x; v[4 * o + 1] = f.y; v[4 * o + 2] = f.z; v[4 * o + 3] = f.w;
+  }
+#pragma unroll
+  for (int h = 4; h < 128; h <<= 1) {  // register distance 4*2^s <-> element stride 128*2^s
+#pragma unroll
+    for (int j = 0; j < 128; ++j) {
+      if ((j & h) == 0) {
+        const float a = v[j], b = v[j + h];
+        v[j] = a + b;
+        v[j + h] = a - b;
+      }
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 128; ++j) {
+    v[j] *= 0.015625f;  // / sqrt(4096): exact, same bits as the division
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+#pragma unroll
+  for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
+  float s = __fdiv_rn(amax, 7.f);
+  if (s == 0.f) s = 1e-3f;
+  if (lane == 0) sa[token] = s;
+  if (OUT == 1) {
+    uint32_t* d8 = reinterpret_cast<uint32_t*>(qa + size_t(token) * 4096);
+#pragma unroll
+    for (int o = 0; o < 32; ++o) d8[o * 32 + lane] = pack4_int8x16(v + 4 * o, s);
+  } else {
+    uint16_t* d4 = reinterpret_cast<uint16_t*>(qa + size_t(token) * 2048);
+#pragma unroll
+    for (int o = 0; o < 32; ++o) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) w |= (uint32_t(quant1(v[4 * o + c], s)) & 0xFu) << (4 * c);
+      d4[o * 32 + lane] = uint16_t(w);
+    }
+  }
+}
+
+template <int OUT>
+static int launch_quant(const uint16_t* xp, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int bf16,
+                        cudaStream_t stream) {
   const int blocks = int((M + kQuantWarps - 1) / kQuantWarps);
-  const int bf16 = dtype == ASRQ_BF16;
+  const int thr = kQuantWarps * 32;
   if (!hadamard) {
     if (K % 8 || K <= 0) return fail(ASRQ_ERR_SHAPE, "quant_int4: K %% 8 != 0 (K=%lld)", (long long)K);
-    quant_int4_kernel<<<blocks, kQuantWarps * 32, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16);
+    quant_int4_kernel<OUT><<<blocks, thr, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16);
   } else {
     switch (K) {
-      case 256: hadamard_quant_kernel<8><<<blocks, kQuantWarps * 32, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
-      case 512: hadamard_quant_kernel<16><<<blocks, kQuantWarps * 32, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
-      case 1024: hadamard_quant_kernel<32><<<blocks, kQuantWarps * 32, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
-      case 2048: hadamard_quant_kernel<64><<<blocks, kQuantWarps * 32, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
-      case 4096: hadamard_quant_kernel<128><<<blocks, kQuantWarps * 32, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
+      case 256: hadamard_quant_kernel<8, OUT><<<blocks, thr, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
+      case 512: hadamard_quant_kernel<16, OUT><<<blocks, thr, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
+      case 1024: hadamard_quant_kernel<32, OUT><<<blocks, thr, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
+      case 2048: hadamard_quant_kernel<64, OUT><<<blocks, thr, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
+      case 4096: {
+        const int smem = kQuantWarps * 16384;
+        ASRQ_CUDA_TRY(cudaFuncSetAttribute(hadamard4096_quant_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        hadamard4096_quant_kernel<OUT><<<blocks, thr, smem, stream>>>(xp, qa, sa, int(M), bf16);
+        break;
+      }
       default:
         return fail(ASRQ_ERR_SHAPE, "hadamard_quant_int4: K must be 256, 512, 1024, 2048 or 4096 (K=%lld)",
                     (long long)K);
@@ -164,6 +291,16 @@ int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_
   }
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;
+}
+
+// out_int8 = 0: qa receives packed nibbles (M x K/2); 1: int8 holding 16*q (M x K).
+int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
+                        int out_int8, cudaStream_t stream) {
+  if (M <= 0) return ASRQ_OK;
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const int bf16 = dtype == ASRQ_BF16;
+  return out_int8 ? launch_quant<1>(xp, qa, sa, M, K, hadamard, bf16, stream)
+                  : launch_quant<0>(xp, qa, sa, M, K, hadamard, bf16, stream);
 }
 
 }  // namespace asrq

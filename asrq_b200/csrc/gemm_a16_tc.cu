@@ -17,6 +17,7 @@
 // stage reusable); accf[b]/acce[b] hand the accumulator buffers back and forth.
 // Every wait is bounded (tcgen05.cuh).
 #include <algorithm>
+#include <cstdlib>
 
 #include "tcgen05.cuh"
 
@@ -58,23 +59,22 @@ __device__ __forceinline__ void dequant_word(uint32_t q, uint32_t s2, uint32_t z
         out[2 * j + 1] = h2_as_u32(__hfma2(c1, u32_as_h2(s2), u32_as_h2(z2)));
       }
     } else {
-      const uint32_t magic = 0x43004300u;  // 128 | field (7 mantissa bits)
-      const __nv_bfloat162 k128 = *reinterpret_cast<const __nv_bfloat162*>(&magic);
-      const __nv_bfloat162 sb = *reinterpret_cast<const __nv_bfloat162*>(&s2);
-      const __nv_bfloat162 zb = *reinterpret_cast<const __nv_bfloat162*>(&z2);
+      // bf16 activations: exact codes via the fp16 trick, q*scale+zero in fp32, one rounding to bf16
+      // (s2, z2 carry the fp32 scale and zero bit patterns in this mode).
+      const uint32_t magic = 0x64006400u;
+      const float sf = __uint_as_float(s2), zf = __uint_as_float(z2);
       if (BITS == 4) {
-        uint32_t r = lop3_and_or(t >> 4, 0x000f0000u, magic);
-        r = lop3_and_or(t, 0x0000000fu, r);
-        const __nv_bfloat162 c = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&r), k128);
-        const __nv_bfloat162 w = __hfma2(c, sb, zb);
+        const uint32_t v = lop3_and_or(t, 0x00f0000fu, magic);
+        const float2 c = __half22float2(__hfma2(u32_as_h2(v), u32_as_h2(0x2c003c00u), u32_as_h2(0xd400e400u)));
+        const __nv_bfloat162 w = __floats2bfloat162_rn(fmaf(c.x, sf, zf), fmaf(c.y, sf, zf));
         out[j] = *reinterpret_cast<const uint32_t*>(&w);
       } else {
-        uint32_t r0 = lop3_and_or(t >> 2, 0x00030000u, magic);
-        r0 = lop3_and_or(t, 0x00000003u, r0);
-        uint32_t r1 = lop3_and_or(t >> 6, 0x00030000u, magic);
-        r1 = lop3_and_or(t >> 4, 0x00000003u, r1);
-        const __nv_bfloat162 w0 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&r0), k128), sb, zb);
-        const __nv_bfloat162 w1 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&r1), k128), sb, zb);
+        const uint32_t v0 = lop3_and_or(t, 0x000c0003u, magic);
+        const uint32_t v1 = lop3_and_or(t, 0x00c00030u, magic);
+        const float2 c0 = __half22float2(__hfma2(u32_as_h2(v0), u32_as_h2(0x34003c00u), u32_as_h2(0xdc00e400u)));
+        const float2 c1 = __half22float2(__hfma2(u32_as_h2(v1), u32_as_h2(0x24002c00u), u32_as_h2(0xcc00d400u)));
+        const __nv_bfloat162 w0 = __floats2bfloat162_rn(fmaf(c0.x, sf, zf), fmaf(c0.y, sf, zf));
+        const __nv_bfloat162 w1 = __floats2bfloat162_rn(fmaf(c1.x, sf, zf), fmaf(c1.y, sf, zf));
         out[2 * j] = *reinterpret_cast<const uint32_t*>(&w0);
         out[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&w1);
       }
@@ -184,24 +184,34 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
   } else if (warp < 6) {
     // ------------------------------ dequant ------------------------------
     const int t = threadIdx.x - 64;
-    uint32_t it = 0;
+    const int my_tiles = (ntiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+    const uint32_t total = uint32_t(my_tiles) * uint32_t(nkb);
+    // scale and zero of this thread's row for flat iteration i (tile-major, then K block), packed
+    auto load_sz = [&](uint32_t i) -> uint32_t {
+      const int tile = int(blockIdx.x) + int(i / nkb) * int(gridDim.x);
+      const int kb = int(i % nkb);
+      const size_t idx = (size_t(tile % p.n_ftiles) * 128 + t) * p.groups_per_row + (kb * 64) / p.group_size;
+      return uint32_t(__half_as_ushort(__ldg(p.scales + idx))) | (uint32_t(__half_as_ushort(__ldg(p.zeros + idx))) << 16);
+    };
+    constexpr int PFD = 4;  // K blocks of look-ahead for the scale/zero loads
+    uint32_t szq[PFD];
+#pragma unroll
+    for (int i = 0; i < PFD; ++i) szq[i] = (uint32_t(i) < total) ? load_sz(i) : 0u;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      const int ft = tile % p.n_ftiles;
-      const size_t row = size_t(ft) * 128 + t;
-      const __half* sc = p.scales + row * p.groups_per_row;
-      const __half* zr = p.zeros + row * p.groups_per_row;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+    for (uint32_t it0 = 0; it0 < total && ok; it0 += PFD) {
+#pragma unroll
+      for (int u = 0; u < PFD; ++u) {
+        const uint32_t it = it0 + u;
+        if (it >= total || !ok) break;
         const int s = it % nst;
         const uint32_t ph = (it / nst) & 1u;
-        const int gi = (kb * 64) / p.group_size;
-        const __half sh = __ldg(sc + gi), zh = __ldg(zr + gi);
+        const uint32_t sz = szq[u];
+        if (it + PFD < total) szq[u] = load_sz(it + PFD);
+        const __half sh = __ushort_as_half(uint16_t(sz & 0xffffu)), zh = __ushort_as_half(uint16_t(sz >> 16));
         uint32_t s2, z2;
         if (BF16) {
-          const __nv_bfloat162 sb2 = __float2bfloat162_rn(__half2float(sh));
-          const __nv_bfloat162 zb2 = __float2bfloat162_rn(__half2float(zh));
-          s2 = *reinterpret_cast<const uint32_t*>(&sb2);
-          z2 = *reinterpret_cast<const uint32_t*>(&zb2);
+          s2 = __float_as_uint(__half2float(sh));
+          z2 = __float_as_uint(__half2float(zh));
         } else {
           s2 = h2_as_u32(__half2half2(sh));
           z2 = h2_as_u32(__half2half2(zh));
@@ -273,6 +283,10 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
 // Token-tile width: the multiple of 32 (<= 256, <= M) that minimises
 // rounds-over-the-SMs x (tile width + fixed per-tile overhead).
 int gemm_tc_pick_bt(int64_t M, int64_t N, int sm_count) {
+  if (const char* e = getenv("ASRQ_B200_TC_BT")) {  // tuning knob: force the token-tile width
+    const int v = atoi(e);
+    if (v >= 32 && v <= 256 && v % 32 == 0) return v;
+  }
   int best = 32;
   double best_cost = 1e30;
   const int64_t nft = N / 128;

@@ -2,11 +2,12 @@
 //
 // Two steps per call, both on the caller's stream:
 //
-//  1. expand: packed signed nibbles -> int8 holding 16x the value (E = (q << 4) & 0xf0..,
-//     O = q & 0xf0..; the k order inside each 8-k word pair is (even k, odd k) for both
-//     operands, which a contraction does not care about).  Weights N x K and activations
-//     M x K go to the caller's workspace.  A product is 256x the true one; the factor is
-//     folded into the weight scale (an exact power of two).
+//  1. expand: packed signed nibbles -> int8 holding 16x the value, natural k order
+//     ((q << 4) & 0xf0f0f0f0 gives the even k, q & 0xf0f0f0f0 the odd k, one byte permute
+//     interleaves them).  Weights N x K and activations M x K go to the caller's workspace;
+//     the fused LinearQQ entry skips the activation pass because its prologue writes this
+//     format directly.  A product is 256x the true one; the factor is folded into the
+//     weight scale (an exact power of two).
 //
 //  2. GEMM: one persistent block per SM.  Weight tile = MMA A operand (128 features = TMEM
 //     lanes), activation tile = B operand (BT tokens = TMEM columns), both int8 K-major with
@@ -28,13 +29,17 @@ __global__ void __launch_bounds__(256)
 expand_int4_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n_vec) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
     const uint4 q = __ldg(src + i);
-    uint4 lo, hi;
-    lo.x = (q.x << 4) & 0xf0f0f0f0u; lo.y = q.x & 0xf0f0f0f0u;
-    lo.z = (q.y << 4) & 0xf0f0f0f0u; lo.w = q.y & 0xf0f0f0f0u;
-    hi.x = (q.z << 4) & 0xf0f0f0f0u; hi.y = q.z & 0xf0f0f0f0u;
-    hi.z = (q.w << 4) & 0xf0f0f0f0u; hi.w = q.w & 0xf0f0f0f0u;
-    dst[2 * i] = lo;
-    dst[2 * i + 1] = hi;
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t e = (w[j] << 4) & 0xf0f0f0f0u;  // 16 * (k0, k2, k4, k6)
+      const uint32_t d = w[j] & 0xf0f0f0f0u;         // 16 * (k1, k3, k5, k7)
+      o[2 * j] = prmt(e, d, 0x5140);                 // k0 k1 k2 k3
+      o[2 * j + 1] = prmt(e, d, 0x7362);             // k4 k5 k6 k7
+    }
+    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
   }
 }
 
@@ -248,26 +253,21 @@ bool w4a4_gemm_tc_supports(int64_t M, int64_t N, int64_t K, int group_size) {
 }
 
 size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  return kStatusBytes + 768 + size_t(N) * K + size_t(M) * K;
+  return 1024 + size_t(N) * K + ((size_t(M) * K + 255) & ~size_t(255)) + size_t(M) * sizeof(float) + 256;
 }
 
-int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias, void* y,
-                 int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
-  if (workspace_bytes < w4a4_tc_workspace_bytes(M, N, K))
-    return fail(ASRQ_ERR_WORKSPACE, "w4a4 gemm: workspace %zu < %zu bytes", workspace_bytes,
-                w4a4_tc_workspace_bytes(M, N, K));
-  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w4a4 gemm: size");
-  uint8_t* w8 = static_cast<uint8_t*>(workspace) + 1024;
-  uint8_t* a8 = w8 + size_t(N) * K;
-  const size_t nvec_w = size_t(N) * K / 32, nvec_a = size_t(M) * K / 32;
-  const int eb = sm_count * 8;
-  expand_int4_kernel<<<int(std::min<size_t>(eb, (nvec_w + 255) / 256)), 256, 0, stream>>>(
-      reinterpret_cast<const uint4*>(qw), reinterpret_cast<uint4*>(w8), nvec_w);
-  expand_int4_kernel<<<int(std::min<size_t>(eb, (nvec_a + 255) / 256)), 256, 0, stream>>>(
-      reinterpret_cast<const uint4*>(qa), reinterpret_cast<uint4*>(a8), nvec_a);
+int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int sm_count, cudaStream_t stream) {
+  const size_t nvec = n_elems / 32;
+  const int blocks = int(std::max<size_t>(1, std::min<size_t>(size_t(sm_count) * 8, (nvec + 255) / 256)));
+  expand_int4_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), nvec);
   ASRQ_CUDA_TRY(cudaGetLastError());
+  return ASRQ_OK;
+}
 
+// GEMM proper on int8 (16x) operands already in global memory.
+int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const void* sw, const void* bias,
+                          void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                          void* workspace, int sm_count, cudaStream_t stream) {
   W4A4TcParams p;
   p.sa = sa;
   p.sw = static_cast<const __half*>(sw);
@@ -304,6 +304,42 @@ int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const vo
   }
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;
+}
+
+// workspace: [0,1024) status | W8 (N*K) | A8 (M*K) | sA (M floats, fused entry only)
+int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias, void* y,
+                 int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+  if (workspace_bytes < w4a4_tc_workspace_bytes(M, N, K))
+    return fail(ASRQ_ERR_WORKSPACE, "w4a4 gemm: workspace %zu < %zu bytes", workspace_bytes,
+                w4a4_tc_workspace_bytes(M, N, K));
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w4a4 gemm: size");
+  uint8_t* w8 = static_cast<uint8_t*>(workspace) + 1024;
+  uint8_t* a8 = w8 + size_t(N) * K;
+  int rc = expand_int4(qw, w8, size_t(N) * K, sm_count, stream);
+  if (rc) return rc;
+  if ((rc = expand_int4(qa, a8, size_t(M) * K, sm_count, stream))) return rc;
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, sm_count, stream);
+}
+
+int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
+                        int out_int8, cudaStream_t stream);
+
+// LinearQQ.forward in one call: the prologue writes int8 activations straight into the workspace.
+int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void* bias, void* y, int64_t M, int64_t N,
+                   int64_t K, int group_size, int hadamard, int dtype, void* workspace, size_t workspace_bytes,
+                   int sm_count, cudaStream_t stream) {
+  if (workspace_bytes < w4a4_tc_workspace_bytes(M, N, K))
+    return fail(ASRQ_ERR_WORKSPACE, "w4a4 linear: workspace %zu < %zu bytes", workspace_bytes,
+                w4a4_tc_workspace_bytes(M, N, K));
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w4a4 linear: size");
+  uint8_t* w8 = static_cast<uint8_t*>(workspace) + 1024;
+  uint8_t* a8 = w8 + size_t(N) * K;
+  float* sa = reinterpret_cast<float*>(a8 + ((size_t(M) * K + 255) & ~size_t(255)));
+  int rc = hadamard_quant_int4(x, a8, sa, M, K, hadamard, dtype, 1, stream);
+  if (rc) return rc;
+  if ((rc = expand_int4(qw, w8, size_t(N) * K, sm_count, stream))) return rc;
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, nullptr, M, N, K, group_size, dtype, workspace, sm_count, stream);
 }
 
 }  // namespace asrq

@@ -189,19 +189,54 @@ class LinearQQ(LinearQ):
         q = torch.stack((lo, hi), dim=-1).reshape(qa.shape[0], -1).to(torch.float32)
         return q, sa.reshape(-1, 1)
 
-    def forward(self, input, acc_dump=None):
+    def _prepared_weight(self) -> torch.Tensor:
+        """int8 operand form of ``weight`` (16x the code, natural k order), derived on first use and
+        whenever the packed buffer is replaced or modified; not part of ``state_dict``."""
+        key = (self.weight.data_ptr(), self.weight._version, self.weight.device)
+        if getattr(self, "_w8_key", None) != key:
+            n, k = self.out_features, self.in_features
+            w8 = torch.empty((n, k), dtype=torch.uint8, device=self.weight.device)
+            _lib.call("asrq_w4a4_prepare_weight", self.weight.data_ptr(), w8.data_ptr(), n, k,
+                      torch.cuda.current_stream(self.weight.device).cuda_stream)
+            self._w8, self._w8_key = w8, key
+        return self._w8
+
+    def _tensor_core_ok(self, m: int) -> bool:
+        n, k, g = self.out_features, self.in_features, self.group_size
+        return m >= 64 and n % 128 == 0 and k % 128 == 0 and g % 128 == 0 and k % g == 0
+
+    def forward(self, input, acc_dump=None, two_call=False):
+        """``two_call=True`` forces the packed-activation sequence (asrq_hadamard_quant_int4 then
+        asrq_w4a4_gemm); the default for large M is the prologue writing int8 operands directly.
+        Both produce the same bits."""
         self._check_buffers(input)
         if input.numel() == 0:
             _require_cuda_16bit(input, "LinearQQ")
             return input.new_empty(*input.shape[:-1], self.out_features)
-        qa, sa, dt, stream = self._quantize(input)
-        m, n, k = qa.shape[0], self.out_features, self.in_features
-        y = torch.empty((m, n), dtype=input.dtype, device=input.device)
-        ws = _workspace(input.device, _lib.workspace_bytes(_lib.WS_W4A4_GEMM, m, n, k))
-        _lib.call("asrq_w4a4_gemm", qa.data_ptr(), sa.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
-                  None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
-                  None if acc_dump is None else acc_dump.data_ptr(), m, n, k, self.group_size, dt,
-                  ws.data_ptr(), ws.numel(), stream)
+        n, k = self.out_features, self.in_features
+        bias = None if self.bias is None else self.bias.data_ptr()
+        dump = None if acc_dump is None else acc_dump.data_ptr()
+        if two_call or not self._tensor_core_ok(input.numel() // k):
+            qa, sa, dt, stream = self._quantize(input)
+            m = qa.shape[0]
+            y = torch.empty((m, n), dtype=input.dtype, device=input.device)
+            ws = _workspace(input.device, _lib.workspace_bytes(_lib.WS_W4A4_GEMM, m, n, k))
+            _lib.call("asrq_w4a4_gemm", qa.data_ptr(), sa.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
+                      bias, y.data_ptr(), dump, m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
+        else:
+            dt = _require_cuda_16bit(input, "LinearQQ")
+            x2 = _as_2d(input, k)
+            m = x2.shape[0]
+            w8 = self._prepared_weight()
+            a8 = torch.empty((m, k), dtype=torch.uint8, device=input.device)
+            sa = torch.empty((m,), dtype=torch.float32, device=input.device)
+            y = torch.empty((m, n), dtype=input.dtype, device=input.device)
+            ws = _workspace(input.device, _lib.STATUS_BYTES)
+            stream = torch.cuda.current_stream(input.device).cuda_stream
+            _lib.call("asrq_hadamard_quant_int8", x2.data_ptr(), a8.data_ptr(), sa.data_ptr(), m, k,
+                      1 if self.hadamard else 0, dt, stream)
+            _lib.call("asrq_w4a4_gemm_int8", a8.data_ptr(), sa.data_ptr(), w8.data_ptr(), self.scales.data_ptr(),
+                      bias, y.data_ptr(), dump, m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
         if _CHECK:
             check_status(input.device)
         return y.reshape(*input.shape[:-1], n)

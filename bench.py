@@ -140,7 +140,8 @@ class W4A4Config2(Workload):
         nsets = max(2, (2 * L2_BYTES) // x.numel() // 2 + 1)
         gen = torch.Generator(device="cpu").manual_seed(seed + 1)
         self.xs = [x] + [x[torch.randperm(self.M, generator=gen).to(device)].contiguous() for _ in range(nsets - 1)]
-        self.qa = torch.empty(self.M, self.K // 2, dtype=torch.uint8, device=device)
+        self.a8 = torch.empty(self.M, self.K, dtype=torch.uint8, device=device)
+        self.w8 = self.layer._prepared_weight()  # int8 operand form of the weights, derived once at load
         self.sa = torch.empty(self.M, dtype=torch.float32, device=device)
         self.y = torch.empty(self.M, self.N, dtype=torch.float16, device=device)
         self.ws = torch.zeros(_lib.workspace_bytes(_lib.WS_W4A4_GEMM, self.M, self.N, self.K), dtype=torch.uint8,
@@ -154,10 +155,10 @@ class W4A4Config2(Workload):
 
     # algorithmic bytes of the two kernels
     def prologue_bytes(self):
-        return self.M * self.K * 2 + self.M * self.K // 2 + self.M * 4
+        return self.M * self.K * 2 + self.M * self.K + self.M * 4  # x in, int8 operand out, scales out
 
     def gemm_bytes(self):
-        return self.M * self.K // 2 + self.N * self.K // 2 + self.N * (self.K // self.G) * 2 + self.M * 4 + self.M * self.N * 2
+        return self.M * self.K + self.N * self.K + self.N * (self.K // self.G) * 2 + self.M * 4 + self.M * self.N * 2
 
     def step(self, i, ev=None):
         st = torch.cuda.current_stream().cuda_stream
@@ -165,17 +166,17 @@ class W4A4Config2(Workload):
         L = self.layer
         if ev:
             ev[0].record()
-        self.lib.call("asrq_hadamard_quant_int4", x.data_ptr(), self.qa.data_ptr(), self.sa.data_ptr(), self.M, self.K,
+        self.lib.call("asrq_hadamard_quant_int8", x.data_ptr(), self.a8.data_ptr(), self.sa.data_ptr(), self.M, self.K,
                       1, self.lib.F16, st)
         if ev:
             ev[1].record()
-        self.lib.call("asrq_w4a4_gemm", self.qa.data_ptr(), self.sa.data_ptr(), L.weight.data_ptr(),
+        self.lib.call("asrq_w4a4_gemm_int8", self.a8.data_ptr(), self.sa.data_ptr(), self.w8.data_ptr(),
                       L.scales.data_ptr(), L.bias.data_ptr(), self.y.data_ptr(), None, self.M, self.N, self.K, self.G,
                       self.lib.F16, self.ws.data_ptr(), self.ws.numel(), st)
         if ev:
             ev[2].record()
 
-    kernels = [("hadamard_quant_int4", 0, 1), ("w4a4_gemm", 1, 2)]
+    kernels = [("hadamard_quant_int8", 0, 1), ("w4a4_gemm", 1, 2)]
 
     def e2e_step(self, i):
         xh = self.x_host[i % len(self.x_host)]
@@ -190,8 +191,8 @@ class W4A4Config2(Workload):
                "peak": int8_tops, "peak_source": "torch._int_mm 8192^3 timed in this run (int8 is not in MEASURED_PEAKS.json)",
                "frac": ach / int8_tops if int8_tops else None,
                "frac_of_2x_bf16_measured": ach / (2 * peaks["bf16_tflops"]), "traffic": None}
-        pro = self.prologue_bytes() / (kernel_ms["hadamard_quant_int4"] * 1e-3) / 1e9
-        out["prologue"] = {"kernel": "hadamard_quant_int4", "bound": "hbm", "achieved": pro, "unit": "GB/s",
+        pro = self.prologue_bytes() / (kernel_ms["hadamard_quant_int8"] * 1e-3) / 1e9
+        out["prologue"] = {"kernel": "hadamard4096_quant_kernel", "bound": "hbm", "achieved": pro, "unit": "GB/s",
                            "peak": peaks["hbm_gbs"], "frac": pro / peaks["hbm_gbs"], "of": peaks["source"]}
         return out
 
@@ -322,22 +323,41 @@ class DecodeSweepConfig3(Workload):
         self.copies = 2
         self.items2 = [dict(it, w=it["w"].clone(), s=it["s"].clone(), z=it["z"].clone()) for it in self.items]
         self.launches_per_step = len(self.items)
+        self.graphs = None
         self.ws = torch.zeros(_lib.workspace_bytes(_lib.WS_LINEARQ, 16, 6144, 6144), dtype=torch.uint8, device=device)
-        self.l2_note = (f"{len(self.items)} launches per step, each on its own weight copy "
+        self.l2_note = (f"{len(self.items)} launches per step replayed as one CUDA graph, each on its own weight copy "
                         f"({2 * total >> 20} MiB over two alternating sets > 126 MiB L2)")
 
     def units_per_step(self):
         return float(self.total_bytes)
 
-    def step(self, i, ev=None):
+    def _launch_all(self, items):
         st = torch.cuda.current_stream().cuda_stream
-        items = self.items if i % 2 == 0 else self.items2
-        if ev:
-            ev[0].record()
         for it in items:
             self.lib.call(f"asrq_w{it['bits']}a16_gemv", it["x"].data_ptr(), it["w"].data_ptr(), it["s"].data_ptr(),
                           it["z"].data_ptr(), None, it["y"].data_ptr(), it["m"], it["n"], it["k"], self.G,
                           self.lib.F16, self.ws.data_ptr(), self.ws.numel(), st)
+
+    def _graphs(self):
+        """The 30 launches of one step captured once per weight set: a decode step is launch-bound
+        when issued call by call from Python, so it is replayed as a CUDA graph."""
+        if self.graphs is None:
+            self._launch_all(self.items)
+            self._launch_all(self.items2)
+            torch.cuda.synchronize()
+            self.graphs = []
+            for items in (self.items, self.items2):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._launch_all(items)
+                self.graphs.append(g)
+        return self.graphs
+
+    def step(self, i, ev=None):
+        g = self._graphs()[i % 2]
+        if ev:
+            ev[0].record()
+        g.replay()
         if ev:
             ev[1].record()
 

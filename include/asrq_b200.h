@@ -115,7 +115,7 @@ int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scal
  * symmetric int4 quantisation  s = absmax/7 (0 -> 1e-3),  q = rint(v/s)  with
  * IEEE fp32 division (asrq/quantizers/activation.py:26-28, asrq/core/linear.py:77-82).
  * Writes qa[M,K/2] (signed nibbles, even k low) and sa[M] (fp32).
- * hadamard != 0 requires K a power of two, 256 <= K <= 8192; otherwise K % 8 == 0.
+ * hadamard != 0 requires K in {256, 512, 1024, 2048, 4096}; otherwise K % 8 == 0.
  * Replaces per_token_quant_int4 (asrq/matmulq/csrc/bindings.cpp:69-72).
  */
 int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K,
@@ -128,7 +128,9 @@ int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, i
  * qa[M,K/2], qw[N,K/2] signed-nibble packed; sw[N,K/group_size] fp16; sa[M] fp32.
  * If acc_dump is not NULL the int32 group sums are also written to
  * acc_dump[M,N,K/group_size] (for exactness checks).
- * Requires N % 128 == 0, group_size == 128 (or 64), K % group_size == 0.
+ * Requires N % 64 == 0, K % 128 == 0, group_size % 128 == 0, K % group_size == 0; the tcgen05
+ * kernel takes M >= 64 and N % 128 == 0, other shapes run on a register-tile kernel.
+ * Workspace: asrq_workspace_bytes(ASRQ_WS_W4A4_GEMM, M, N, K) (holds the int8 operands).
  * Replaces matmul_wxax / matmul_w4a4 / matmul_int4_rescale
  * (asrq/matmulq/csrc/bindings.cpp:29-43, 552-605, 652-703).
  */
@@ -136,6 +138,40 @@ int asrq_w4a4_gemm(const uint8_t* qa, const float* sa, const uint8_t* qw, const 
                    const void* bias, void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K,
                    int group_size, int dtype, void* workspace, size_t workspace_bytes,
                    void* stream);
+
+/*
+ * LinearQQ.forward in one call: the prologue above (writing int8 activations straight into the
+ * workspace instead of packed nibbles) followed by the GEMM above.  Same integer codes, same
+ * int32 group sums and therefore the same output bits as the two-call sequence.
+ * x[M,K] fp16/bf16; qw[N,K/2] signed nibbles; sw[N,K/group_size] fp16; y[M,N].
+ * Requires N % 128 == 0, K % 128 == 0, group_size % 128 == 0; with hadamard != 0, K in
+ * {256, 512, 1024, 2048, 4096}.  Workspace: asrq_workspace_bytes(ASRQ_WS_W4A4_GEMM, M, N, K).
+ * Replaces matmul_wxax, which likewise took f16 activations and quantised them into scratch
+ * (asrq/matmulq/csrc/bindings.cpp:37-43, 552-605).
+ */
+int asrq_w4a4_linear(const void* x, const uint8_t* qw, const void* sw, const void* bias, void* y,
+                     int64_t M, int64_t N, int64_t K, int group_size, int hadamard, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The three steps of asrq_w4a4_linear as separate calls, for callers that keep the expanded
+ * weight resident (it depends only on the weights) or want to time the steps:
+ *   asrq_w4a4_prepare_weight  qw[N,K/2] signed nibbles -> w8[N,K] int8 holding 16x the value, natural
+ *                             k order: the operand format of the tcgen05 kind::i8 kernel.  Done once
+ *                             per layer; counterpart of unpack_int4_to_int8 (bindings.cpp:79-80, 373-400).
+ *   asrq_hadamard_quant_int8  the prologue, writing a8[M,K] in that same format plus sa[M].
+ *                             Same codes as asrq_hadamard_quant_int4 (a8 byte = 16 * code).
+ *   asrq_w4a4_gemm_int8       the GEMM on operands in that format; arguments otherwise as
+ *                             asrq_w4a4_gemm; workspace >= 256 bytes (status block only).
+ *                             Requires N % 128 == 0, K % 128 == 0, group_size % 128 == 0.
+ */
+int asrq_w4a4_prepare_weight(const uint8_t* qw, uint8_t* w8, int64_t N, int64_t K, void* stream);
+int asrq_hadamard_quant_int8(const void* x, uint8_t* a8, float* sa, int64_t M, int64_t K,
+                             int hadamard, int dtype, void* stream);
+int asrq_w4a4_gemm_int8(const uint8_t* a8, const float* sa, const uint8_t* w8, const void* sw,
+                        const void* bias, void* y, int32_t* acc_dump, int64_t M, int64_t N,
+                        int64_t K, int group_size, int dtype, void* workspace,
+                        size_t workspace_bytes, void* stream);
 
 /*
  * Reads the workspace status block back (this one DOES synchronise the stream).

@@ -64,6 +64,30 @@ def test_quant_matches_reference_fixture():
     assert torch.equal(O.unpack_signed_int4(qa), q) and torch.equal(sa, s.reshape(-1))
 
 
+@pytest.mark.parametrize("k,had", [(4096, True), (1024, True), (1280, False)])
+def test_int8_operand_output_matches_packed_codes(k, had):
+    """asrq_hadamard_quant_int8 writes 16 * code per byte, the same codes as the packed entry point."""
+    gen = torch.Generator().manual_seed(k + 1)
+    x = (torch.randn(70, k, generator=gen) * 2).half()
+    qa, sa = _quant_gpu(x, had)
+    xd = x.to(DEV)
+    a8 = torch.empty(70, k, dtype=torch.uint8, device=DEV)
+    s8 = torch.empty(70, dtype=torch.float32, device=DEV)
+    _lib.call("asrq_hadamard_quant_int8", xd.data_ptr(), a8.data_ptr(), s8.data_ptr(), 70, k, int(had), _lib.F16,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    codes = O.unpack_signed_int4(qa).to(torch.int32)
+    assert torch.equal(a8.cpu().view(torch.int8).to(torch.int32), codes * 16)
+    assert torch.equal(s8.cpu(), sa)
+    # and the weight-side expansion
+    w = torch.randint(-8, 8, (128, k), generator=gen)
+    pw = O.pack_signed_int4(w).to(DEV)
+    w8 = torch.empty(128, k, dtype=torch.uint8, device=DEV)
+    _lib.call("asrq_w4a4_prepare_weight", pw.data_ptr(), w8.data_ptr(), 128, k, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(w8.cpu().view(torch.int8).to(torch.int64), w * 16)
+
+
 def test_hadamard_rejects_bad_k():
     x = torch.zeros(4, 768, dtype=torch.float16, device=DEV)
     qa = torch.empty(4, 384, dtype=torch.uint8, device=DEV)
@@ -93,7 +117,7 @@ def _w4a4_case(m, k, n, g, seed, bias=True, outliers=True):
     (48, 1024, 64, 256, True),       # wider group, narrow N: register-tile kernel
 ])
 def test_w4a4_gemm_exact_accumulators_and_output(m, k, n, g, bias):
-    x, w, b = _w4a4_case(m, k, n, g, seed=m + k)
+    x, w, b = _w4a4_case(m, k, n, g, seed=m + k, bias=bias)
     had = (k & (k - 1)) == 0
     qa_ref, sa_ref, pa_ref = O.hadamard_quant_int4(x, had)
     codes, sw, pw = O.prepare_w4a4_weight(w, g, had)
@@ -111,9 +135,21 @@ def test_w4a4_gemm_exact_accumulators_and_output(m, k, n, g, bias):
     asrq_b200.check_status()
     assert torch.equal(acc.cpu(), acc_ref), "int32 group accumulators differ"
     assert_close_rows(y, y_ref, what=f"w4a4 m{m} k{k} n{n}")
-    # and without the dump
+    # without the dump, through the packed two-call sequence and through the one-call entry point:
+    # the same codes and the same int32 sums give the same output bits
     y2 = lq(x.to(DEV))
     assert torch.equal(y2, y)
+    y3 = lq(x.to(DEV), two_call=True)
+    assert torch.equal(y3, y)
+    if n % 128 == 0 and g % 128 == 0:
+        xd = x.to(DEV)
+        y4 = torch.empty(m, n, dtype=torch.float16, device=DEV)
+        ws = torch.zeros(_lib.workspace_bytes(_lib.WS_W4A4_GEMM, m, n, k), dtype=torch.uint8, device=DEV)
+        _lib.call("asrq_w4a4_linear", xd.data_ptr(), lq.weight.data_ptr(), lq.scales.data_ptr(),
+                  None if lq.bias is None else lq.bias.data_ptr(), y4.data_ptr(), m, n, k, g, int(had), _lib.F16,
+                  ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+        _lib.call("asrq_check_status", ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert torch.equal(y4, y)
     qf, sf = lq.quantize_activation(x.to(DEV))
     assert torch.equal(qf.cpu(), qa_ref.float()) and torch.equal(sf.cpu().reshape(-1), sa_ref)
 
