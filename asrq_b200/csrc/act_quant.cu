@@ -21,13 +21,35 @@ __device__ __forceinline__ float in16_to_float(uint16_t b, bool bf16) {
   return bf16 ? bf16_bits_to_float(b) : __half2float(__ushort_as_half(b));
 }
 
-__device__ __forceinline__ int quant1(float v, float s) {
-  float q = rintf(__fdiv_rn(v, s));
-  q = fminf(fmaxf(q, -7.f), 7.f);
-  return int(q);
+// Per-token scale and its reciprocal.
+struct QScale {
+  float s, inv;
+};
+
+// rint(v / s) with IEEE division, bit for bit, without a division per element: r = v * (1/s) is
+// within 1.3e-6 of the correctly rounded quotient (|r| <= 7), so both round to the same integer
+// unless r lies within 1e-5 of a tie; only then is the true quotient computed.  Rounding to
+// nearest-even is done by adding 1.5 * 2^23, which also leaves the two's-complement code in the
+// low mantissa bits, so there is no float->int conversion either.  |code| <= 7 by construction
+// (s = absmax / 7), as in the reference formula, which has no clamp.
+__device__ __forceinline__ int quant1(float v, QScale qs) {
+  const float magic = 12582912.f;
+  const float r = __fmul_rn(v, qs.inv);
+  float t = __fadd_rn(r, magic);
+  const float d = fabsf(__fsub_rn(r, __fsub_rn(t, magic)));
+  if (d > 0.49999f) t = __fadd_rn(rintf(__fdiv_rn(v, qs.s)), magic);
+  return __float_as_int(t) - 0x4B400000;
 }
 
-__device__ __forceinline__ uint32_t pack8_int4(const float* v, float s) {
+__device__ __forceinline__ QScale make_qscale(float amax) {
+  QScale q;
+  q.s = __fdiv_rn(amax, 7.f);
+  if (q.s == 0.f) q.s = 1e-3f;
+  q.inv = __fdiv_rn(1.f, q.s);
+  return q;
+}
+
+__device__ __forceinline__ uint32_t pack8_int4(const float* v, QScale s) {
   uint32_t w = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) w |= (uint32_t(quant1(v[i], s)) & 0xFu) << (4 * i);
@@ -35,7 +57,7 @@ __device__ __forceinline__ uint32_t pack8_int4(const float* v, float s) {
 }
 
 // Four codes as int8 bytes holding 16x the value (the operand format of the tcgen05 W4A4 GEMM).
-__device__ __forceinline__ uint32_t pack4_int8x16(const float* v, float s) {
+__device__ __forceinline__ uint32_t pack4_int8x16(const float* v, QScale s) {
   uint32_t w = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) w |= ((uint32_t(quant1(v[i], s)) << 4) & 0xFFu) << (8 * i);
@@ -93,9 +115,8 @@ hadamard_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa,
   }
 #pragma unroll
   for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
-  float s = __fdiv_rn(amax, 7.f);
-  if (s == 0.f) s = 1e-3f;
-  if (lane == 0) sa[token] = s;
+  const QScale s = make_qscale(amax);
+  if (lane == 0) sa[token] = s.s;
   if (OUT == 1) {
     uint32_t* d8 = reinterpret_cast<uint32_t*>(qa + size_t(token) * K + lane * V);
     if (V >= 16) {
@@ -149,9 +170,8 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
   }
 #pragma unroll
   for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
-  float s = __fdiv_rn(amax, 7.f);
-  if (s == 0.f) s = 1e-3f;
-  if (lane == 0) sa[token] = s;
+  const QScale s = make_qscale(amax);
+  if (lane == 0) sa[token] = s.s;
   uint32_t* dst = reinterpret_cast<uint32_t*>(qa + size_t(token) * (OUT == 1 ? K : K / 2));
   for (int i = lane; i < units; i += 32) {
     const uint4 u = __ldg(src + i);
@@ -245,9 +265,8 @@ hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ 
   }
 #pragma unroll
   for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
-  float s = __fdiv_rn(amax, 7.f);
-  if (s == 0.f) s = 1e-3f;
-  if (lane == 0) sa[token] = s;
+  const QScale s = make_qscale(amax);
+  if (lane == 0) sa[token] = s.s;
   if (OUT == 1) {
     uint32_t* d8 = reinterpret_cast<uint32_t*>(qa + size_t(token) * 4096);
 #pragma unroll

@@ -2,19 +2,23 @@
 //
 // The weight tile is the MMA "A" operand (128 output features = 128 TMEM lanes), the
 // activation tile is the "B" operand (BT tokens = BT TMEM columns, BT <= 256 chosen
-// by the host).  One persistent block per SM, ten warps:
+// by the host).  One persistent block per SM, eighteen warps:
 //
 //   warp 0      TMA producer: per 64-wide K block, one tile of activations
 //               (BT x 64, 128-byte swizzle) and one tile of packed weights (128 rows).
 //   warp 1      MMA issuer: tcgen05.mma kind::f16, 4 x (128 x BT x 16) per K block,
 //               fp32 accumulators in TMEM, two accumulator buffers of 256 columns.
-//   warps 2-5   dequant: one weight row per thread; packed words -> fp16/bf16 in
+//   warps 2-13  dequant, three groups of four warps; group d takes the K blocks with
+//               index % 3 == d, one weight row per thread: packed words -> fp16/bf16 in
 //               registers -> q*scale+zero -> the swizzled K-major A tile in shared memory.
-//   warps 6-9   epilogue: tcgen05.ld of the previous tile's accumulator, + bias,
+//               (One group alone is latency-bound: a single warp per scheduler cannot hide
+//               its own instruction latencies, and the MMA pipe then idles 70% of the time.)
+//   warps 14-17 epilogue: tcgen05.ld of the previous tile's accumulator, + bias,
 //               convert, store, while the next tile's main loop runs.
 //
-// Rings: full[s] (TMA landed) -> deq[s] (A tile written) -> MMA -> empty[s] (MMA done,
-// stage reusable); accf[b]/acce[b] hand the accumulator buffers back and forth.
+// Rings: full[s] (TMA landed) -> deq[a] (A slot a = K block % 3 written) -> MMA -> empty[s]
+// (TMA stage reusable) and afree[a] (A slot reusable); accf[b]/acce[b] hand the accumulator
+// buffers back and forth.
 // Every wait is bounded (tcgen05.cuh).
 #include <algorithm>
 #include <cstdlib>
@@ -32,7 +36,8 @@ struct GemmTcParams {
   int M, N, K, group_size, groups_per_row, bt, nstages, n_ftiles, n_ttiles;
 };
 
-constexpr int kTcThreads = 320;
+constexpr int kTcDequantGroups = 3;
+constexpr int kTcThreads = 32 * (2 + 4 * kTcDequantGroups + 4);
 constexpr int kTcMaxStages = 8;
 constexpr uint32_t kATileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
 constexpr uint32_t kWSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
@@ -87,30 +92,36 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
                    const GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[3 * kTcMaxStages + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kTcMaxStages + 2 * kTcDequantGroups + 4];
   __shared__ uint32_t tmem_slot;
 
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t xbytes = uint32_t(p.bt) * 128u;
-  const uint32_t stage_bytes = xbytes + kATileBytes + kWSlotBytes;
+  // [A tile x kTcDequantGroups] [TMA stage: activations (bt x 128 B) + packed weights] x nstages
+  constexpr uint32_t a_ring_bytes = kTcDequantGroups * kATileBytes;
+  const uint32_t stage_bytes = xbytes + kWSlotBytes;
   constexpr uint32_t wbytes = 128u * 8u * BITS;
   const int nst = p.nstages;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = tc::smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto deq_bar = [&](int s) { return bar0 + 8u * (kTcMaxStages + s); };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (2 * kTcMaxStages + s); };
-  auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kTcMaxStages + b); };
-  auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kTcMaxStages + 2 + b); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kTcMaxStages + s); };
+  auto deq_bar = [&](int a) { return bar0 + 8u * (2 * kTcMaxStages + a); };                       // A slot written
+  auto afree_bar = [&](int a) { return bar0 + 8u * (2 * kTcMaxStages + kTcDequantGroups + a); };  // A slot consumed
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kTcMaxStages + 2 * kTcDequantGroups + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kTcMaxStages + 2 * kTcDequantGroups + 2 + b); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
       tc::mbar_init(full_bar(s), 1);
-      tc::mbar_init(deq_bar(s), 128);
       tc::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < kTcDequantGroups; ++a) {
+      tc::mbar_init(deq_bar(a), 128);
+      tc::mbar_init(afree_bar(a), 1);
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(accf_bar(b), 1);
@@ -144,10 +155,10 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           const int s = it % nst;
           const uint32_t ph = (it / nst) & 1u;
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
-          const uint32_t sb = base + s * stage_bytes;
+          const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
           tc::mbar_arrive_expect_tx(full_bar(s), xbytes + wbytes);
           tc::tma_load_2d(sb, &tmx, kb * 64, tt * p.bt, full_bar(s));
-          tc::tma_load_2d(sb + xbytes + kATileBytes, &tmw, kb * 8 * BITS, ft * 128, full_bar(s));
+          tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, ft * 128, full_bar(s));
         }
       }
     }
@@ -165,25 +176,29 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % nst;
           const uint32_t ph = (it / nst) & 1u;
-          if (!tc::mbar_wait(full_bar(s), ph, p.status, 3) || !tc::mbar_wait(deq_bar(s), ph, p.status, 4)) {
+          const int a = it % kTcDequantGroups;
+          const uint32_t dph = (it / kTcDequantGroups) & 1u;
+          if (!tc::mbar_wait(full_bar(s), ph, p.status, 3) || !tc::mbar_wait(deq_bar(a), dph, p.status, 4)) {
             ok = false;
             break;
           }
           tc::fence_after_sync();
-          const uint32_t sb = base + s * stage_bytes;
-          const uint32_t a_addr = sb + xbytes, b_addr = sb;
+          const uint32_t a_addr = base + a * kATileBytes, b_addr = base + a_ring_bytes + s * stage_bytes;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             tc::mma_f16(d_tmem, tc::smem_desc_sw128(a_addr + 32u * k), tc::smem_desc_sw128(b_addr + 32u * k),
                         idesc, uint32_t((kb | k) != 0));
           tc::mma_commit(empty_bar(s));
+          tc::mma_commit(afree_bar(a));
         }
         if (ok) tc::mma_commit(accf_bar(buf));
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + 4 * kTcDequantGroups) {
     // ------------------------------ dequant ------------------------------
-    const int t = threadIdx.x - 64;
+    const int t = (threadIdx.x - 64) & 127;           // weight row inside the tile
+    const uint32_t dgroup = (threadIdx.x - 64) >> 7;  // which K blocks this warp group takes
+    constexpr uint32_t NDG = kTcDequantGroups;
     const int my_tiles = (ntiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
     const uint32_t total = uint32_t(my_tiles) * uint32_t(nkb);
     // scale and zero of this thread's row for flat iteration i (tile-major, then K block), packed
@@ -196,17 +211,17 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
     constexpr int PFD = 4;  // K blocks of look-ahead for the scale/zero loads
     uint32_t szq[PFD];
 #pragma unroll
-    for (int i = 0; i < PFD; ++i) szq[i] = (uint32_t(i) < total) ? load_sz(i) : 0u;
+    for (int i = 0; i < PFD; ++i) szq[i] = (dgroup + NDG * i < total) ? load_sz(dgroup + NDG * i) : 0u;
     bool ok = true;
-    for (uint32_t it0 = 0; it0 < total && ok; it0 += PFD) {
+    for (uint32_t it0 = dgroup; it0 < total && ok; it0 += NDG * PFD) {
 #pragma unroll
       for (int u = 0; u < PFD; ++u) {
-        const uint32_t it = it0 + u;
+        const uint32_t it = it0 + NDG * u;
         if (it >= total || !ok) break;
         const int s = it % nst;
         const uint32_t ph = (it / nst) & 1u;
         const uint32_t sz = szq[u];
-        if (it + PFD < total) szq[u] = load_sz(it + PFD);
+        if (it + NDG * PFD < total) szq[u] = load_sz(it + NDG * PFD);
         const __half sh = __ushort_as_half(uint16_t(sz & 0xffffu)), zh = __ushort_as_half(uint16_t(sz >> 16));
         uint32_t s2, z2;
         if (BF16) {
@@ -216,10 +231,14 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           s2 = h2_as_u32(__half2half2(sh));
           z2 = h2_as_u32(__half2half2(zh));
         }
-        if (!tc::mbar_wait(full_bar(s), ph, p.status, 5)) { ok = false; break; }
-        uint8_t* sb = smem + s * stage_bytes;
-        const uint4* wp = reinterpret_cast<const uint4*>(sb + xbytes + kATileBytes + t * (8 * BITS));
-        uint8_t* arow = sb + xbytes + t * 128;
+        // this group's A slot must have been consumed by the MMAs of its previous K block
+        if (!tc::mbar_wait(afree_bar(dgroup), ((it / NDG) & 1u) ^ 1u, p.status, 7) ||
+            !tc::mbar_wait(full_bar(s), ph, p.status, 5)) {
+          ok = false;
+          break;
+        }
+        const uint4* wp = reinterpret_cast<const uint4*>(smem + a_ring_bytes + s * stage_bytes + xbytes + t * (8 * BITS));
+        uint8_t* arow = smem + dgroup * kATileBytes + t * 128;
         constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
@@ -239,7 +258,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           }
         }
         tc::fence_proxy_async_smem();
-        tc::mbar_arrive(deq_bar(s));
+        tc::mbar_arrive(deq_bar(dgroup));
       }
     }
   } else {
@@ -339,10 +358,10 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
   p.bt = gemm_tc_pick_bt(M, N, sm_count);
   p.n_ftiles = int(N / 128);
   p.n_ttiles = int((M + p.bt - 1) / p.bt);
-  const size_t stage_bytes = size_t(p.bt) * 128 + kATileBytes + kWSlotBytes;
-  const size_t budget = 227 * 1024 - 1024 - 512;
+  const size_t stage_bytes = size_t(p.bt) * 128 + kWSlotBytes;
+  const size_t budget = 227 * 1024 - 1024 - 512 - kTcDequantGroups * kATileBytes;
   p.nstages = int(std::min<size_t>(kTcMaxStages, budget / stage_bytes));
-  const size_t smem = 1024 + p.nstages * stage_bytes;
+  const size_t smem = 1024 + kTcDequantGroups * kATileBytes + p.nstages * stage_bytes;
 
   const bool bf16 = dtype == ASRQ_BF16;
   CUtensorMap tmx, tmw;

@@ -1,14 +1,18 @@
 // Decode path: y[M,N] = x[M,K] . dequant(W)[N,K]^T for M <= 16 per launch.
 //
-// HBM-bound skinny GEMM.  A warp owns a strip of 16 weight rows over one K slice:
-// each lane streams 128-bit words of packed weights for two rows (rows g and g+8,
-// g = lane/4), turns them into fp16 in registers (exact integer code, then one
-// fused multiply-add with the group scale and offset) and uses them as the A
-// operand of mma.sync.m16n8k16; the activations (B operand, up to 16 tokens) sit
-// in shared memory in the element order the unpacking produces, so no shuffles are
-// needed.  K is split across gridDim.y; partial sums go to the caller's workspace
-// and the last block to arrive for a row tile adds them in slice order, so the
-// result does not depend on scheduling.
+// HBM-bound skinny GEMM.  A warp owns a strip of 16 weight rows over one K span: each lane
+// streams 128-bit words of packed weights for two rows (rows g and g+8, g = lane/4), turns
+// them into fp16 in registers (exact integer code, then one fused multiply-add with the
+// group scale and offset) and uses them as the A operand of mma.sync.m16n8k16; the
+// activations (B operand, up to 16 tokens) sit in shared memory in the element order the
+// unpacking produces, so no shuffles are needed.
+//
+// K is split twice so that every weight byte of the layer is requested in the first
+// microsecond: KQ warps of a block share a row strip and each take a quarter (or half, or
+// all) of the block's K slice, their partial tiles are added through shared memory in a
+// fixed order; and, only where the layer has too few rows to fill the SMs, gridDim.y blocks
+// split K further through the caller's workspace, the last block to arrive for a row tile
+// adding the slices in slice order.  The result never depends on scheduling.
 #include <algorithm>
 
 #include "common.cuh"
@@ -24,11 +28,10 @@ struct GemvParams {
   uint16_t* y;
   float* partials;
   unsigned* counters;
-  int M, N, K, group_size, groups_per_row, S, kslice, bf16;
+  int M, N, K, group_size, groups_per_row, S, kslice, KQ, bf16;
 };
 
 constexpr int kGemvWarps = 8;
-constexpr int kGemvRows = kGemvWarps * 16;  // weight rows per block
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                              uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -54,15 +57,53 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
   constexpr int UPT = KPT / 8;       // 16-byte activation units per lane per step
   constexpr int NH = 32 / BITS / 2;  // half2 values per 32-bit weight word
   constexpr int MR = 8 * MH;         // token rows held in shared memory
+  constexpr int PF = 3;              // steps of weights in flight ahead of the math
+  constexpr int FR = 4 * MH;         // accumulator registers per lane
 
   extern __shared__ uint4 xs[];
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
-  const int k_begin = blockIdx.y * p.kslice;
-  const int row_units = p.kslice / 8 + 4;  // +64 B: rows g and g+1 land on different banks
+  const int KQ = p.KQ;
+  const int strips = kGemvWarps / KQ;  // row strips per block
+  const int strip = warp / KQ, kq = warp - strip * KQ;
+  const int rows_per_block = strips * 16;
+  const int k_begin = blockIdx.y * p.kslice;  // block's K slice
+  const int wslice = p.kslice / KQ;           // this warp's span inside it
+  const int row_units = p.kslice / 8 + 4;     // +64 B: rows g and g+1 land on different banks
+  const int n_base = blockIdx.x * rows_per_block + strip * 16;
+  const bool active = n_base < p.N;
+  const int nchunks = wslice / CHUNK;
+  const int chunk0 = kq * nchunks;  // first step of this warp inside the block's slice
 
-  // ---- stage the activation slice, re-ordered to the unpacking order -------------
+  // ---- weights, scales and zeros first: they do not depend on the staged activations ----------
+  const int r0 = n_base + g, r1 = r0 + 8;
+  const size_t row_bytes = size_t(p.K) * BITS / 8;
+  const int kw = k_begin + kq * wslice + c * KPT;  // first k of this lane
+  const uint8_t* w0 = p.w + size_t(r0) * row_bytes + size_t(kw) * BITS / 8;
+  const uint8_t* w1 = p.w + size_t(r1) * row_bytes + size_t(kw) * BITS / 8;
+  const __half* sc0 = p.scales + size_t(r0) * p.groups_per_row;
+  const __half* sc1 = p.scales + size_t(r1) * p.groups_per_row;
+  const __half* zr0 = p.zeros + size_t(r0) * p.groups_per_row;
+  const __half* zr1 = p.zeros + size_t(r1) * p.groups_per_row;
+  uint4 qa[PF + 1], qb[PF + 1];
+  __half sa[PF + 1], sb[PF + 1], za[PF + 1], zb[PF + 1];
+  auto issue = [&](int chunk, int slot) {
+    qa[slot] = ldg_stream_v4(w0 + size_t(chunk) * (CHUNK * BITS / 8));
+    qb[slot] = ldg_stream_v4(w1 + size_t(chunk) * (CHUNK * BITS / 8));
+    const int gi = (kw + chunk * CHUNK) / p.group_size;
+    sa[slot] = __ldg(sc0 + gi);
+    za[slot] = __ldg(zr0 + gi);
+    sb[slot] = __ldg(sc1 + gi);
+    zb[slot] = __ldg(zr1 + gi);
+  };
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < PF; ++i)
+      if (i < nchunks) issue(i, i);
+  }
+
+  // ---- stage the block's activation slice, re-ordered to the unpacking order ------------------
   {
     const int blocks16 = p.kslice / 16;
     for (int i = tid; i < MR * blocks16; i += blockDim.x) {
@@ -103,45 +144,21 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
   }
   __syncthreads();
 
-  const int n_base = blockIdx.x * kGemvRows + warp * 16;
   float acc[MH][4];
 #pragma unroll
   for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[mh][i] = 0.f;
 
-  if (n_base < p.N) {
-    const int r0 = n_base + g, r1 = r0 + 8;
-    const size_t row_bytes = size_t(p.K) * BITS / 8;
-    const uint8_t* w0 = p.w + r0 * row_bytes + size_t(k_begin + c * KPT) * BITS / 8;
-    const uint8_t* w1 = p.w + r1 * row_bytes + size_t(k_begin + c * KPT) * BITS / 8;
-    const __half* sc0 = p.scales + size_t(r0) * p.groups_per_row;
-    const __half* sc1 = p.scales + size_t(r1) * p.groups_per_row;
-    const __half* zr0 = p.zeros + size_t(r0) * p.groups_per_row;
-    const __half* zr1 = p.zeros + size_t(r1) * p.groups_per_row;
-    const int nchunks = p.kslice / CHUNK;
-    constexpr int PF = 2;  // chunks of weights in flight ahead of the math
-    uint4 qa[PF + 1], qb[PF + 1];
-#pragma unroll
-    for (int i = 0; i < PF; ++i) {
-      if (i < nchunks) {
-        qa[i] = ldg_stream_v4(w0 + size_t(i) * (CHUNK * BITS / 8));
-        qb[i] = ldg_stream_v4(w1 + size_t(i) * (CHUNK * BITS / 8));
-      }
-    }
-    for (int chunk0 = 0; chunk0 < nchunks; chunk0 += PF + 1) {
+  if (active) {
+    for (int cbase = 0; cbase < nchunks; cbase += PF + 1) {
 #pragma unroll
       for (int u = 0; u < PF + 1; ++u) {
-        const int chunk = chunk0 + u;
+        const int chunk = cbase + u;
         if (chunk < nchunks) {
-          const int nxt = chunk + PF;
-          if (nxt < nchunks) {
-            qa[(u + PF) % (PF + 1)] = ldg_stream_v4(w0 + size_t(nxt) * (CHUNK * BITS / 8));
-            qb[(u + PF) % (PF + 1)] = ldg_stream_v4(w1 + size_t(nxt) * (CHUNK * BITS / 8));
-          }
-          const int gi = (k_begin + chunk * CHUNK + c * KPT) / p.group_size;
-          const __half2 s0 = __half2half2(__ldg(sc0 + gi)), z0 = __half2half2(__ldg(zr0 + gi));
-          const __half2 s1 = __half2half2(__ldg(sc1 + gi)), z1 = __half2half2(__ldg(zr1 + gi));
+          if (chunk + PF < nchunks) issue(chunk + PF, (u + PF) % (PF + 1));
+          const __half2 s0 = __half2half2(sa[u]), z0 = __half2half2(za[u]);
+          const __half2 s1 = __half2half2(sb[u]), z1 = __half2half2(zb[u]);
           const uint32_t wa[4] = {qa[u].x, qa[u].y, qa[u].z, qa[u].w};
           const uint32_t wb[4] = {qb[u].x, qb[u].y, qb[u].z, qb[u].w};
 #pragma unroll
@@ -158,12 +175,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
             for (int mh = 0; mh < MH; ++mh) {
 #pragma unroll
               for (int t = 0; t < NH / 4; ++t) {
-                const uint4 xb =
-                    xs[(g + 8 * mh) * row_units + (chunk * UPT + j * (NH / 4) + t) * 4 + c];
-                mma_m16n8k16(acc[mh], h2_as_u32(ha[4 * t]), h2_as_u32(hb[4 * t]),
-                             h2_as_u32(ha[4 * t + 1]), h2_as_u32(hb[4 * t + 1]), xb.x, xb.y);
-                mma_m16n8k16(acc[mh], h2_as_u32(ha[4 * t + 2]), h2_as_u32(hb[4 * t + 2]),
-                             h2_as_u32(ha[4 * t + 3]), h2_as_u32(hb[4 * t + 3]), xb.z, xb.w);
+                const uint4 xb = xs[(g + 8 * mh) * row_units + ((chunk0 + chunk) * UPT + j * (NH / 4) + t) * 4 + c];
+                mma_m16n8k16(acc[mh], h2_as_u32(ha[4 * t]), h2_as_u32(hb[4 * t]), h2_as_u32(ha[4 * t + 1]),
+                             h2_as_u32(hb[4 * t + 1]), xb.x, xb.y);
+                mma_m16n8k16(acc[mh], h2_as_u32(ha[4 * t + 2]), h2_as_u32(hb[4 * t + 2]), h2_as_u32(ha[4 * t + 3]),
+                             h2_as_u32(hb[4 * t + 3]), xb.z, xb.w);
               }
             }
           }
@@ -172,40 +188,39 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
     }
   }
 
-  // ---- epilogue --------------------------------------------------------------------
-  // acc[mh][0..1]: weight row n_base+g, tokens 8*mh+2c, +1;  acc[mh][2..3]: row n_base+g+8.
-  if (p.S == 1) {
-    if (n_base < p.N) {
+  // ---- add the KQ partial tiles of each strip through shared memory (fixed order) --------------
+  // acc[mh][i] of lane (g, c): weight row strip*16 + g + 8*(i>>1), token 8*mh + 2c + (i&1).
+  __syncthreads();  // everyone is done reading xs
+  float* red = reinterpret_cast<float*>(xs);
 #pragma unroll
-      for (int mh = 0; mh < MH; ++mh)
+  for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int n = n_base + g + (i >> 1) * 8;
-          const int m = 8 * mh + 2 * c + (i & 1);
-          if (m < p.M) {
-            float v = acc[mh][i];
-            if (p.bias) v += __half2float(__ldg(p.bias + n));
-            p.y[size_t(m) * p.N + n] = float_to_out16(v, p.bf16);
-          }
-        }
-    }
-    return;
-  }
+    for (int i = 0; i < 4; ++i) red[(warp * FR + mh * 4 + i) * 32 + lane] = acc[mh][i];
+  __syncthreads();
 
-  if (n_base < p.N) {
-    float* dst = p.partials + size_t(blockIdx.y) * MR * p.N;
-#pragma unroll
-    for (int mh = 0; mh < MH; ++mh)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int n = n_base + g + (i >> 1) * 8;
-        const int m = 8 * mh + 2 * c + (i & 1);
-        if (m < p.M) __stcg(dst + size_t(m) * p.N + n, acc[mh][i]);
+  const int per_strip = FR * 32;
+  const int n_out = strips * per_strip;  // values this block owns
+  __shared__ unsigned is_last;
+  for (int o = tid; o < n_out; o += blockDim.x) {
+    const int st = o / per_strip, rem = o - st * per_strip;
+    float v = 0.f;
+    for (int q = 0; q < KQ; ++q) v += red[(st * KQ + q) * per_strip + rem];
+    const int fi = rem >> 5, l = rem & 31;
+    const int n = blockIdx.x * rows_per_block + st * 16 + (l >> 2) + ((fi >> 1) & 1) * 8;
+    const int m = 8 * (fi >> 2) + 2 * (l & 3) + (fi & 1);
+    if (n < p.N && m < p.M) {
+      if (p.S == 1) {
+        if (p.bias) v += __half2float(__ldg(p.bias + n));
+        p.y[size_t(m) * p.N + n] = float_to_out16(v, p.bf16);
+      } else {
+        __stcg(p.partials + (size_t(blockIdx.y) * MR + m) * p.N + n, v);
       }
+    }
   }
+  if (p.S == 1) return;
+
   __threadfence();
   __syncthreads();
-  __shared__ unsigned is_last;
   if (tid == 0) {
     const unsigned ticket = atomicAdd(p.counters + blockIdx.x, 1u);
     is_last = (ticket == unsigned(p.S) - 1u);
@@ -213,14 +228,22 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  const int n0 = blockIdx.x * kGemvRows;
-  const int ncols = min(kGemvRows, p.N - n0);
-  for (int i = tid; i < p.M * kGemvRows; i += blockDim.x) {
-    const int m = i / kGemvRows, nn = i - m * kGemvRows;
+  const int n0 = blockIdx.x * rows_per_block;
+  const int ncols = min(rows_per_block, p.N - n0);
+  for (int i = tid; i < p.M * rows_per_block; i += blockDim.x) {
+    const int m = i / rows_per_block, nn = i - m * rows_per_block;
     if (nn < ncols) {
       const int n = n0 + nn;
+      const float* src = p.partials + size_t(m) * p.N + n;
+      const size_t sstride = size_t(MR) * p.N;
       float v = 0.f;
-      for (int s = 0; s < p.S; ++s) v += __ldcg(p.partials + (size_t(s) * MR + m) * p.N + n);
+      int s = 0;
+      for (; s + 4 <= p.S; s += 4) {  // four independent loads, added in slice order
+        const float a0 = __ldcg(src + (s + 0) * sstride), a1 = __ldcg(src + (s + 1) * sstride);
+        const float a2 = __ldcg(src + (s + 2) * sstride), a3 = __ldcg(src + (s + 3) * sstride);
+        v += a0; v += a1; v += a2; v += a3;
+      }
+      for (; s < p.S; ++s) v += __ldcg(src + s * sstride);
       if (p.bias) v += __half2float(__ldg(p.bias + n));
       p.y[size_t(m) * p.N + n] = float_to_out16(v, p.bf16);
     }
@@ -228,26 +251,42 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
   if (tid == 0) p.counters[blockIdx.x] = 0;
 }
 
-// Number of K slices for one launch: enough blocks to cover the SMs about twice, a
-// slice no longer than 2048 (shared-memory footprint), partial-sum traffic at most a
-// quarter of the weight bytes, and a divisor of the number of 128-bit steps.
-int gemv_pick_split(int bits, int mrows, int64_t N, int64_t K, int sm_count) {
+// How one launch splits K.  T = S * KQ spans per row strip, chosen as the smallest divisor of
+// the number of 128-bit steps such that (a) a warp has at most four steps, so all its loads
+// are in flight at once, and (b) the grid has at least one block per SM.  KQ of them (at
+// most 4, fewer for larger M so that re-staging the activations stays cheap) are taken
+// inside a block; the remaining S go through the workspace.
+struct GemvSplit {
+  int S, KQ;
+};
+
+GemvSplit gemv_pick_split(int bits, int m, int64_t N, int64_t K, int sm_count) {
   const int chunk = (128 / bits) * 4;
   const int nchunks = int(K / chunk);
-  const int ntiles = int((N + kGemvRows - 1) / kGemvRows);
-  int want = (2 * sm_count + ntiles - 1) / ntiles;
-  const int traffic_cap = int(std::max<int64_t>(1, K * bits / (128 * int64_t(mrows))));
-  want = std::min(want, traffic_cap);
-  want = std::min(want, std::min(nchunks, kGemvMaxSplit));
-  const int need = int((K + 2047) / 2048);
-  want = std::max(want, need);
-  int s = std::max(1, want);
-  while (s < nchunks && nchunks % s) ++s;
-  if (s > kGemvMaxSplit) {  // fall back to the largest divisor within the limit
-    s = kGemvMaxSplit;
-    while (s > 1 && nchunks % s) --s;
+  const int64_t strips = (N + 15) / 16;
+  int t_min = std::max((nchunks + 3) / 4, int((int64_t(sm_count) * kGemvWarps + strips - 1) / strips));
+  t_min = std::min(std::max(t_min, 1), nchunks);
+  int T = t_min;
+  while (T < nchunks && nchunks % T) ++T;
+  const int kq_cap = m <= 4 ? 4 : (m <= 8 ? 2 : 1);
+  int KQ = 1;
+  for (int q = kq_cap; q >= 1; q >>= 1)
+    if (T % q == 0) {
+      KQ = q;
+      break;
+    }
+  int S = T / KQ;
+  // the block's slice is staged in shared memory: keep it at or below 2048
+  while (K / S > 2048 && S < nchunks) {
+    ++S;
+    while (S < nchunks && (nchunks % S || (nchunks / S) % KQ)) ++S;
   }
-  return s;
+  if (S > kGemvMaxSplit || (nchunks % S) || (nchunks / S) % KQ) {  // fall back to the plainest legal split
+    KQ = 1;
+    S = std::min(kGemvMaxSplit, nchunks);
+    while (S > 1 && nchunks % S) --S;
+  }
+  return {S, KQ};
 }
 
 size_t gemv_workspace_bytes(int64_t N) {
@@ -255,15 +294,15 @@ size_t gemv_workspace_bytes(int64_t N) {
 }
 
 template <int BITS, int MH>
-static int launch_gemv(const GemvParams& p, int ntiles, cudaStream_t stream) {
-  const size_t smem = size_t(8 * MH) * (p.kslice / 8 + 4) * 16;
+static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
+  const size_t xs_bytes = size_t(8 * MH) * (p.kslice / 8 + 4) * 16;
+  const size_t red_bytes = size_t(kGemvWarps) * 4 * MH * 32 * sizeof(float);
+  const size_t smem = std::max(xs_bytes, red_bytes);
   auto kern = gemv_a16_kernel<BITS, MH>;
-  static thread_local size_t configured[4] = {0, 0, 0, 0};
-  size_t& cfg = configured[(BITS == 4 ? 0 : 2) + (MH - 1)];
-  if (smem > 48 * 1024 && smem > cfg) {
+  if (smem > 48 * 1024)
     ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    cfg = smem;
-  }
+  const int rows_per_block = (kGemvWarps / p.KQ) * 16;
+  const int ntiles = (p.N + rows_per_block - 1) / rows_per_block;
   kern<<<dim3(ntiles, p.S), kGemvWarps * 32, smem, stream>>>(p);
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;
@@ -277,8 +316,8 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
     return fail(ASRQ_ERR_SHAPE,
                 "w%da16 gemv: need N%%16==0, K%%%d==0, group_size%%%d==0, K%%group_size==0 "
                 "(N=%lld K=%lld g=%d)", bits, chunk, 128 / bits, (long long)N, (long long)K, group_size);
-  if (N > int64_t(4096) * kGemvRows || K > (1 << 20))
-    return fail(ASRQ_ERR_LIMIT, "w%da16 gemv: N or K too large", bits);
+  if (N > int64_t(4096) * 16 || K > (1 << 20))
+    return fail(ASRQ_ERR_LIMIT, "w%da16 gemv: N > 65536 or K > 2^20", bits);
   if (workspace_bytes < gemv_workspace_bytes(N))
     return fail(ASRQ_ERR_WORKSPACE, "w%da16 gemv: workspace %zu < %zu bytes", bits, workspace_bytes,
                 gemv_workspace_bytes(N));
@@ -294,20 +333,22 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
   p.group_size = group_size;
   p.groups_per_row = int(K / group_size);
   p.bf16 = dtype == ASRQ_BF16;
-  const int ntiles = int((N + kGemvRows - 1) / kGemvRows);
   for (int64_t m0 = 0; m0 < M; m0 += 16) {
     const int mb = int(std::min<int64_t>(16, M - m0));
     const int mh = mb > 8 ? 2 : 1;
     p.x = static_cast<const uint16_t*>(x) + m0 * K;
     p.y = static_cast<uint16_t*>(y) + m0 * N;
     p.M = mb;
-    p.S = gemv_pick_split(bits, 8 * mh, N, K, sm_count);
+    const GemvSplit sp = gemv_pick_split(bits, mb, N, K, sm_count);
+    p.S = sp.S;
+    p.KQ = sp.KQ;
     p.kslice = int(K / p.S);
+    if (p.kslice > 4096) return fail(ASRQ_ERR_LIMIT, "w%da16 gemv: K slice %d too long", bits, p.kslice);
     int rc;
     if (bits == 4)
-      rc = mh == 1 ? launch_gemv<4, 1>(p, ntiles, stream) : launch_gemv<4, 2>(p, ntiles, stream);
+      rc = mh == 1 ? launch_gemv<4, 1>(p, stream) : launch_gemv<4, 2>(p, stream);
     else
-      rc = mh == 1 ? launch_gemv<2, 1>(p, ntiles, stream) : launch_gemv<2, 2>(p, ntiles, stream);
+      rc = mh == 1 ? launch_gemv<2, 1>(p, stream) : launch_gemv<2, 2>(p, stream);
     if (rc) return rc;
   }
   return ASRQ_OK;

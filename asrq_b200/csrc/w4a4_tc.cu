@@ -13,12 +13,15 @@
 //     lanes), activation tile = B operand (BT tokens = TMEM columns), both int8 K-major with
 //     128-byte swizzle, loaded by TMA; a K block is 128 = one row of 128 bytes = 4 MMAs of
 //     K = 32.  Every weight group (group_size / 128 K blocks) gets a fresh int32 accumulator
-//     buffer in TMEM (two buffers, ping-pong); eight drain warps read it back, convert and
+//     buffer in TMEM (two buffers, ping-pong); twelve drain warps read it back, convert and
 //     add float(acc) * sW[feature, group] into fp32 registers while the next group is
 //     multiplied.  After the last group: * sA[token] + bias, convert, store.
 //
 //   warp 0      TMA producer        warp 1      MMA issuer (and TMEM owner)
-//   warps 2-9   drain + epilogue: warp w reads TMEM lanes 32*(w%4).., columns half (w-2)/4.
+//   warps 2-13  drain + epilogue: warp w reads TMEM lanes 32*(w%4).., column third (w-2)/4.
+//               Three warps per scheduler: the drain (one int->float convert and one FMA per
+//               output per group) needs about as many issue slots as the MMAs need cycles, so
+//               it only keeps up if its instruction latencies are hidden.
 #include <algorithm>
 
 #include "tcgen05.cuh"
@@ -53,7 +56,9 @@ struct W4A4TcParams {
   int M, N, K, groups, blocks_per_group, bt, nstages, n_ftiles, n_ttiles, bf16;
 };
 
-constexpr int kW4A4Threads = 320;
+constexpr int kW4A4ColGroups = 3;
+constexpr int kW4A4DrainWarps = 4 * kW4A4ColGroups;
+constexpr int kW4A4Threads = 32 * (2 + kW4A4DrainWarps);
 constexpr int kW4A4MaxStages = 8;
 constexpr uint32_t kW8TileBytes = 128 * 128;
 
@@ -84,7 +89,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(accf_bar(b), 1);
-      tc::mbar_init(acce_bar(b), 256);
+      tc::mbar_init(acce_bar(b), 32 * kW4A4DrainWarps);
     }
     tc::fence_barrier_init();
     tc::fence_proxy_async_smem();
@@ -152,58 +157,50 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
       }
     }
   } else {
-    const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int hcols = p.bt >> 1;     // columns this warp drains (multiple of 32)
-    const int nch = hcols >> 5;      // 32-column chunks: 1..4
+    const int qd = warp & 3;           // TMEM lane quadrant this warp may read
+    const int cg = (warp - 2) >> 2;    // column group 0..2
+    const int wcols = p.bt / kW4A4ColGroups;  // columns this warp drains (multiple of 16, at most 64)
+    const int nch = wcols >> 4;        // 16-column chunks: 1..4
     uint32_t ac = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
       const int f = ft * 128 + qd * 32 + lane;
       const __half* swrow = p.sw + size_t(f) * p.groups;
-      float accf[128];
+      float accf[64];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) accf[i] = 0.f;
-      const int tok0 = tt * p.bt + half * hcols;
+      for (int i = 0; i < 64; ++i) accf[i] = 0.f;
+      const int tok0 = tt * p.bt + cg * wcols;
+      __half s_next = __ldg(swrow);
       for (int gi = 0; gi < p.groups && ok; ++gi, ++ac) {
         const uint32_t buf = ac & 1u, aph = (ac >> 1) & 1u;
-        const float s = __half2float(__ldg(swrow + gi)) * (1.0f / 256.0f);
+        const float s = __half2float(s_next) * (1.0f / 256.0f);  // operands hold 16x the codes
+        if (gi + 1 < p.groups) s_next = __ldg(swrow + gi + 1);
         if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 14)) { ok = false; break; }
         tc::fence_after_sync();
-        const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u + uint32_t(half * hcols);
-        if (!DUMP) {
+        const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u + uint32_t(cg * wcols);
+        uint32_t r[2][16];
+        tc::tmem_ld_32x16(taddr, r[0]);
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            if (ch < nch) {
-              uint32_t r[32];
-              tc::tmem_ld_32x32(taddr + ch * 32, r);
-              tc::tmem_ld_wait();
-              if (ch == nch - 1) {  // buffer fully read: hand it back before the math
-                tc::fence_before_sync();
-                tc::mbar_arrive(acce_bar(buf));
-              }
-#pragma unroll
-              for (int j = 0; j < 32; ++j) accf[ch * 32 + j] = fmaf(__int2float_rn(int(r[j])), s, accf[ch * 32 + j]);
+        for (int ch = 0; ch < 4; ++ch) {
+          if (ch < nch) {
+            tc::tmem_ld_wait();
+            if (ch + 1 < nch) {
+              tc::tmem_ld_32x16(taddr + (ch + 1) * 16, r[(ch + 1) & 1]);
+            } else {  // buffer fully read: hand it back before the math
+              tc::fence_before_sync();
+              tc::mbar_arrive(acce_bar(buf));
             }
-          }
-        } else {
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            if (ch < nch) {
-              uint32_t r[32];
-              tc::tmem_ld_32x32(taddr + ch * 32, r);
-              tc::tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                accf[ch * 32 + j] = fmaf(__int2float_rn(int(r[j])), s, accf[ch * 32 + j]);
-                const int tok = tok0 + ch * 32 + j;
-                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = int(r[j]) >> 8;
+            for (int j = 0; j < 16; ++j) {
+              const int v = int(r[ch & 1][j]);
+              accf[ch * 16 + j] = fmaf(__int2float_rn(v), s, accf[ch * 16 + j]);
+              if (DUMP) {
+                const int tok = tok0 + ch * 16 + j;
+                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = v >> 8;
               }
             }
           }
-          tc::fence_before_sync();
-          tc::mbar_arrive(acce_bar(buf));
         }
       }
       if (!ok) break;
@@ -212,10 +209,10 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
       for (int ch = 0; ch < 4; ++ch) {
         if (ch < nch) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = tok0 + ch * 32 + j;
+          for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + ch * 16 + j;
             if (tok < p.M)
-              p.y[size_t(tok) * p.N + f] = float_to_out16(accf[ch * 32 + j] * __ldg(p.sa + tok) + bias, p.bf16);
+              p.y[size_t(tok) * p.N + f] = float_to_out16(accf[ch * 16 + j] * __ldg(p.sa + tok) + bias, p.bf16);
           }
         }
       }
@@ -231,11 +228,12 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
   }
 }
 
+// Token-tile width: a multiple of 48 (three column groups of 16-column chunks), at most 192.
 static int w4a4_pick_bt(int64_t M, int64_t N, int sm_count) {
-  int best = 64;
+  int best = 48;
   double best_cost = 1e30;
   const int64_t nft = N / 128;
-  for (int bt = 64; bt <= 256; bt += 64) {
+  for (int bt = 48; bt <= 192; bt += 48) {
     const int64_t tiles = nft * ((M + bt - 1) / bt);
     const int64_t rounds = (tiles + sm_count - 1) / sm_count;
     const double cost = double(rounds) * (bt + 16);
