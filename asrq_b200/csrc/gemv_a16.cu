@@ -14,6 +14,7 @@
 // split K further through the caller's workspace, the last block to arrive for a row tile
 // adding the slices in slice order.  The result never depends on scheduling.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -97,11 +98,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_a16_kernel(const GemvPar
     sb[slot] = __ldg(sc1 + gi);
     zb[slot] = __ldg(zr1 + gi);
   };
+  // Let the next kernel on the stream start as early as possible, and start streaming weights
+  // before this one's own predecessor has finished: weights, scales and zeros are constants,
+  // only the activations, the output and the workspace depend on earlier kernels.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (active) {
 #pragma unroll
     for (int i = 0; i < PF; ++i)
       if (i < nchunks) issue(i, i);
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- stage the block's activation slice, re-ordered to the unpacking order ------------------
   {
@@ -303,8 +309,20 @@ static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
     ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   const int rows_per_block = (kGemvWarps / p.KQ) * 16;
   const int ntiles = (p.N + rows_per_block - 1) / rows_per_block;
-  kern<<<dim3(ntiles, p.S), kGemvWarps * 32, smem, stream>>>(p);
-  ASRQ_CUDA_TRY(cudaGetLastError());
+  // Programmatic dependent launch: consecutive decode kernels overlap their weight fetch with the
+  // predecessor's tail (the kernel orders itself with griddepcontrol.wait).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ntiles, p.S);
+  cfg.blockDim = dim3(kGemvWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  static const bool pdl = getenv("ASRQ_B200_NO_PDL") == nullptr;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
   return ASRQ_OK;
 }
 
