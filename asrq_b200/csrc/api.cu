@@ -13,7 +13,7 @@ namespace asrq {
 // kernels (one translation unit each)
 int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
              void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-             size_t workspace_bytes, int sm_count, cudaStream_t stream);
+             size_t workspace_bytes, int sm_count, cudaStream_t stream, int max_split);
 size_t gemv_workspace_bytes(int64_t N);
 int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
@@ -33,7 +33,7 @@ bool w4a4_gemm_tc_supports(int64_t M, int64_t N, int64_t K, int group_size);
 int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int sm_count, cudaStream_t stream);
 int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const void* sw, const void* bias, void* y,
                    int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                   int sm_count, cudaStream_t stream);
+                   size_t workspace_bytes, int sm_count, cudaStream_t stream);
 size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 // ---- errors -----------------------------------------------------------------------------
@@ -124,7 +124,7 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool bf16, 
   return ASRQ_OK;
 }
 
-static int check_a16_common(const char* who, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+int check_a16_common(const char* who, const void* x, const uint8_t* w, const void* scales, const void* zeros,
                             void* y, int64_t M, int64_t N, int64_t K, int dtype, void* workspace) {
   if (!x || !w || !scales || !zeros || !y) return fail(ASRQ_ERR_NULL, "%s: x, w, scales, zeros and y must not be NULL", who);
   if (!workspace) return fail(ASRQ_ERR_WORKSPACE, "%s: workspace must not be NULL", who);
@@ -132,6 +132,15 @@ static int check_a16_common(const char* who, const void* x, const uint8_t* w, co
   if (M < 0 || N <= 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "%s: M=%lld N=%lld K=%lld", who, (long long)M, (long long)N, (long long)K);
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || !aligned16(workspace))
     return fail(ASRQ_ERR_ALIGN, "%s: x, w, y and workspace must be 16-byte aligned", who);
+  return ASRQ_OK;
+}
+
+// SM count of the current device (checked to be sm_100), for code outside this file.
+int current_device_sm_count(int* sm_count) {
+  const DeviceFacts* f;
+  const int rc = device_facts(&f);
+  if (rc) return rc;
+  *sm_count = f->sm_count;
   return ASRQ_OK;
 }
 
@@ -174,7 +183,7 @@ static int a16_gemv(int bits, const void* x, const uint8_t* w, const void* scale
   if ((rc = device_facts(&f))) return rc;
   if (M == 0) return ASRQ_OK;
   return gemv_a16(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
-                  f->sm_count, static_cast<cudaStream_t>(stream));
+                  f->sm_count, static_cast<cudaStream_t>(stream), kGemvMaxSplit);
 }
 
 static int a16_gemm(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
@@ -324,8 +333,8 @@ int asrq_w4a4_gemm_int8(const uint8_t* a8, const float* sa, const uint8_t* w8, c
   int rc;
   if ((rc = device_facts(&f))) return rc;
   if (M == 0) return ASRQ_OK;
-  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, f->sm_count,
-                        static_cast<cudaStream_t>(stream));
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, workspace_bytes,
+                        f->sm_count, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_check_status(void* workspace, void* stream) {

@@ -33,6 +33,7 @@ struct GemmTcParams {
   const __half* bias;
   uint16_t* y;
   unsigned* status;
+  long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
   int M, N, K, group_size, groups_per_row, bt, nstages, n_ftiles, n_ttiles;
 };
 
@@ -143,6 +144,10 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
 
   const int ntiles = p.n_ftiles * p.n_ttiles;
   const int nkb = p.K / 64;
+  const bool tr = p.trace != nullptr && blockIdx.x == 0;
+  auto mark = [&](int role, uint32_t i, int slot) {
+    if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -155,10 +160,12 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           const int s = it % nst;
           const uint32_t ph = (it / nst) & 1u;
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
+          mark(0, it, 0);
           const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
           tc::mbar_arrive_expect_tx(full_bar(s), xbytes + wbytes);
           tc::tma_load_2d(sb, &tmx, kb * 64, tt * p.bt, full_bar(s));
           tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, ft * 128, full_bar(s));
+          mark(0, it, 1);
         }
       }
     }
@@ -183,6 +190,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
             break;
           }
           tc::fence_after_sync();
+          mark(1, it, 0);
           const uint32_t a_addr = base + a * kATileBytes, b_addr = base + a_ring_bytes + s * stage_bytes;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
@@ -190,6 +198,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
                         idesc, uint32_t((kb | k) != 0));
           tc::mma_commit(empty_bar(s));
           tc::mma_commit(afree_bar(a));
+          mark(1, it, 1);
         }
         if (ok) tc::mma_commit(accf_bar(buf));
       }
@@ -237,6 +246,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           ok = false;
           break;
         }
+        if (t == 0) mark(2, it, 0);
         const uint4* wp = reinterpret_cast<const uint4*>(smem + a_ring_bytes + s * stage_bytes + xbytes + t * (8 * BITS));
         uint8_t* arow = smem + dgroup * kATileBytes + t * 128;
         constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
@@ -259,6 +269,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
         }
         tc::fence_proxy_async_smem();
         tc::mbar_arrive(deq_bar(dgroup));
+        if (t == 0) mark(2, it, 1);
       }
     }
   } else {
@@ -273,6 +284,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
       if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
       tc::fence_after_sync();
+      if (threadIdx.x == kTcThreads - 128) mark(3, tcount, 0);
       const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
       for (int ch = 0; ch < p.bt / 32; ++ch) {
         uint32_t r[32];
@@ -287,6 +299,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       }
       tc::fence_before_sync();
       tc::mbar_arrive(acce_bar(buf));
+      if (threadIdx.x == kTcThreads - 128) mark(3, tcount, 1);
     }
   }
 
@@ -350,6 +363,10 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
   p.bias = static_cast<const __half*>(bias);
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
+  // diagnostic timeline (4 roles x 512 events x 2 clocks), only on request and only if the workspace has room
+  p.trace = (getenv("ASRQ_B200_TRACE") && workspace_bytes >= (1u << 20) + 4 * 512 * 2 * 8)
+                ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20))
+                : nullptr;
   p.M = int(M);
   p.N = int(N);
   p.K = int(K);

@@ -266,7 +266,7 @@ struct GemvSplit {
   int S, KQ;
 };
 
-GemvSplit gemv_pick_split(int bits, int m, int64_t N, int64_t K, int sm_count) {
+GemvSplit gemv_pick_split(int bits, int m, int64_t N, int64_t K, int sm_count, int max_split) {
   const int chunk = (128 / bits) * 4;
   const int nchunks = int(K / chunk);
   const int64_t strips = (N + 15) / 16;
@@ -287,17 +287,18 @@ GemvSplit gemv_pick_split(int bits, int m, int64_t N, int64_t K, int sm_count) {
     ++S;
     while (S < nchunks && (nchunks % S || (nchunks / S) % KQ)) ++S;
   }
-  if (S > kGemvMaxSplit || (nchunks % S) || (nchunks / S) % KQ) {  // fall back to the plainest legal split
+  if (S > max_split || (nchunks % S) || (nchunks / S) % KQ) {  // fall back to the plainest legal split
     KQ = 1;
-    S = std::min(kGemvMaxSplit, nchunks);
+    S = std::min(max_split, nchunks);
     while (S > 1 && nchunks % S) --S;
   }
   return {S, KQ};
 }
 
-size_t gemv_workspace_bytes(int64_t N) {
-  return kPartialOffset + size_t(kGemvMaxSplit) * 16 * size_t(N) * sizeof(float);
+size_t gemv_workspace_bytes(int64_t N, int max_split) {
+  return kPartialOffset + size_t(max_split) * 16 * size_t(N) * sizeof(float);
 }
+size_t gemv_workspace_bytes(int64_t N) { return gemv_workspace_bytes(N, kGemvMaxSplit); }
 
 template <int BITS, int MH>
 static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
@@ -328,7 +329,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
 
 int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
              const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
-             void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+             void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, int max_split) {
   const int chunk = (128 / bits) * 4;
   if (N % 16 || K % chunk || group_size <= 0 || K % group_size || group_size % (128 / bits))
     return fail(ASRQ_ERR_SHAPE,
@@ -336,9 +337,9 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
                 "(N=%lld K=%lld g=%d)", bits, chunk, 128 / bits, (long long)N, (long long)K, group_size);
   if (N > int64_t(4096) * 16 || K > (1 << 20))
     return fail(ASRQ_ERR_LIMIT, "w%da16 gemv: N > 65536 or K > 2^20", bits);
-  if (workspace_bytes < gemv_workspace_bytes(N))
+  if (workspace_bytes < gemv_workspace_bytes(N, max_split))
     return fail(ASRQ_ERR_WORKSPACE, "w%da16 gemv: workspace %zu < %zu bytes", bits, workspace_bytes,
-                gemv_workspace_bytes(N));
+                gemv_workspace_bytes(N, max_split));
   GemvParams p;
   p.w = w;
   p.scales = static_cast<const __half*>(scales);
@@ -357,7 +358,7 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
     p.x = static_cast<const uint16_t*>(x) + m0 * K;
     p.y = static_cast<uint16_t*>(y) + m0 * N;
     p.M = mb;
-    const GemvSplit sp = gemv_pick_split(bits, mb, N, K, sm_count);
+    const GemvSplit sp = gemv_pick_split(bits, mb, N, K, sm_count, max_split);
     p.S = sp.S;
     p.KQ = sp.KQ;
     p.kslice = int(K / p.S);

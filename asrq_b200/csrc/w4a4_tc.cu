@@ -23,6 +23,7 @@
 //               output per group) needs about as many issue slots as the MMAs need cycles, so
 //               it only keeps up if its instruction latencies are hidden.
 #include <algorithm>
+#include <cstdlib>
 
 #include "tcgen05.cuh"
 
@@ -53,6 +54,7 @@ struct W4A4TcParams {
   uint16_t* y;
   int32_t* acc_dump;
   unsigned* status;
+  long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
   int M, N, K, groups, blocks_per_group, bt, nstages, n_ftiles, n_ttiles, bf16;
 };
 
@@ -107,6 +109,10 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
 
   const int ntiles = p.n_ftiles * p.n_ttiles;
   const int nkb = p.K / 128;
+  const bool tr = p.trace != nullptr && blockIdx.x == 0;
+  auto mark = [&](int role, uint32_t i, int slot) {
+    if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -118,10 +124,12 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
           const int s = it % nst;
           const uint32_t ph = (it / nst) & 1u;
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11)) { ok = false; break; }
+          mark(0, it, 0);
           const uint32_t sb = base + s * stage_bytes;
           tc::mbar_arrive_expect_tx(full_bar(s), kW8TileBytes + bbytes);
           tc::tma_load_2d(sb, &tmw, kb * 128, ft * 128, full_bar(s));
           tc::tma_load_2d(sb + kW8TileBytes, &tma, kb * 128, tt * p.bt, full_bar(s));
+          mark(0, it, 1);
         }
       }
     }
@@ -142,6 +150,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
           const uint32_t ph = (it / nst) & 1u;
           if (!tc::mbar_wait(full_bar(s), ph, p.status, 13)) { ok = false; break; }
           tc::fence_after_sync();
+          mark(1, it, 0);
           const uint32_t sb = base + s * stage_bytes;
           const uint32_t d_tmem = tmem_base + buf * 256u;
 #pragma unroll
@@ -149,6 +158,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
             tc::mma_i8(d_tmem, tc::smem_desc_sw128(sb + 32u * k), tc::smem_desc_sw128(sb + kW8TileBytes + 32u * k),
                        idesc, uint32_t((gb | k) != 0));
           tc::mma_commit(empty_bar(s));
+          mark(1, it, 1);
           if (gb == p.blocks_per_group - 1) {
             tc::mma_commit(accf_bar(buf));
             ++ac;
@@ -178,6 +188,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
         if (gi + 1 < p.groups) s_next = __ldg(swrow + gi + 1);
         if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 14)) { ok = false; break; }
         tc::fence_after_sync();
+        if (threadIdx.x == 64) mark(2, ac, 0);
         const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u + uint32_t(cg * wcols);
         uint32_t r[2][16];
         tc::tmem_ld_32x16(taddr, r[0]);
@@ -202,6 +213,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
             }
           }
         }
+        if (threadIdx.x == 64) mark(2, ac, 1);
       }
       if (!ok) break;
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
@@ -265,7 +277,7 @@ int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int sm_count, 
 // GEMM proper on int8 (16x) operands already in global memory.
 int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const void* sw, const void* bias,
                           void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
-                          void* workspace, int sm_count, cudaStream_t stream) {
+                          void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
   W4A4TcParams p;
   p.sa = sa;
   p.sw = static_cast<const __half*>(sw);
@@ -273,6 +285,10 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   p.y = static_cast<uint16_t*>(y);
   p.acc_dump = acc_dump;
   p.status = static_cast<unsigned*>(workspace);
+  // diagnostic timeline (3 roles x 512 events x 2 clocks), only on request and only if the workspace has room
+  p.trace = (getenv("ASRQ_B200_TRACE") && workspace_bytes >= (1u << 20) + 3 * 512 * 2 * 8)
+                ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20))
+                : nullptr;
   p.M = int(M);
   p.N = int(N);
   p.K = int(K);
@@ -317,7 +333,7 @@ int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const vo
   int rc = expand_int4(qw, w8, size_t(N) * K, sm_count, stream);
   if (rc) return rc;
   if ((rc = expand_int4(qa, a8, size_t(M) * K, sm_count, stream))) return rc;
-  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, sm_count, stream);
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, kStatusBytes, sm_count, stream);
 }
 
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
@@ -337,7 +353,7 @@ int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void*
   int rc = hadamard_quant_int4(x, a8, sa, M, K, hadamard, dtype, 1, stream);
   if (rc) return rc;
   if ((rc = expand_int4(qw, w8, size_t(N) * K, sm_count, stream))) return rc;
-  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, nullptr, M, N, K, group_size, dtype, workspace, sm_count, stream);
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, nullptr, M, N, K, group_size, dtype, workspace, kStatusBytes, sm_count, stream);
 }
 
 }  // namespace asrq
