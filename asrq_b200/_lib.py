@@ -46,6 +46,8 @@ SIGNATURES = {
     "asrq_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int64]),
     "asrq_w4a16_gemv": (c_int, _A16_ARGS),
     "asrq_w2a16_gemv": (c_int, _A16_ARGS),
+    "asrq_w4a16_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_int64, c_int, c_int, c_void_p]),
     "asrq_w4a16_gemm": (c_int, _A16_ARGS),
     "asrq_w2a16_gemm": (c_int, _A16_ARGS),
     "asrq_linearq_a16": (c_int, [c_int] + _A16_ARGS),

@@ -374,3 +374,79 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
 }
 
 }  // namespace asrq
+
+// ---------------------------------------------------------------------------------------------
+// asrq_w4a16_gemv_static: the W4A16 decode kernel for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to obtain a workspace: a plugin that is handed input and
+// output buffers by an inference server and is forbidden to call cudaMalloc on the request path, a
+// real-time audio callback, or code that runs after the application has frozen its memory pools.
+// For them the split-K scratch (status block, tile counters, fp32 partial sums) lives in a
+// file-scope device array that every GPU loading the library holds until the process exits.
+//
+// The array's name is only a host-side handle: its device address is fetched once per device with
+// cudaGetSymbolAddress (by the first call made with that device current -- make that first call
+// before any stream capture) and that address is what the kernel receives.  The entry point calls
+// no cudaMalloc, cudaFree or any other allocating routine.  All calls on a device share the one
+// array: the counters and the status block are cleared on the stream at the start of every call,
+// and two calls that overlap on the GPU (different streams) race on it -- serialise them.
+// Limits: N <= 8192 and at most 8 K slices, which bounds the array at 16 640 + 4 Mi bytes.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace asrq {
+
+int check_a16_common(const char* who, const void* x, const uint8_t* w, const void* scales, const void* zeros, void* y,
+                     int64_t M, int64_t N, int64_t K, int dtype, void* workspace);
+int current_device_sm_count(int* sm_count);
+
+constexpr int64_t kStaticMaxN = 8192;
+constexpr int kStaticMaxSplit = 8;
+constexpr size_t kStaticScratchBytes = kPartialOffset + size_t(kStaticMaxSplit) * 16 * kStaticMaxN * sizeof(float);
+
+static __device__ __align__(256) unsigned char g_gemv_scratch[kStaticScratchBytes];
+
+static std::mutex g_scratch_mutex;
+static void* g_scratch_ptr[64];  // device address of g_gemv_scratch, per device ordinal
+
+static int static_scratch(void** out) {
+  int dev = 0;
+  ASRQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(ASRQ_ERR_DEVICE, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    ASRQ_CUDA_TRY(cudaGetSymbolAddress(&p, g_gemv_scratch));
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return ASRQ_OK;
+}
+
+}  // namespace asrq
+
+#pragma GCC visibility push(default)
+extern "C" int asrq_w4a16_gemv_static(const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                                      const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size,
+                                      int dtype, void* stream) {
+  using namespace asrq;
+  last_error().clear();
+  int rc = check_a16_common("asrq_w4a16_gemv_static", x, w, scales, zeros, y, M, N, K, dtype,
+                            /*workspace placeholder, checked non-NULL only*/ const_cast<void*>(x));
+  if (rc) return rc;
+  if (N > kStaticMaxN)
+    return fail(ASRQ_ERR_LIMIT,
+                "asrq_w4a16_gemv_static: N=%lld exceeds the built-in scratch (N <= %lld); use asrq_w4a16_gemv with a "
+                "caller-provided workspace", (long long)N, (long long)kStaticMaxN);
+  int sms = 0;
+  if ((rc = current_device_sm_count(&sms))) return rc;
+  if (M == 0) return ASRQ_OK;
+  void* scratch = nullptr;
+  if ((rc = static_scratch(&scratch))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: status block and tile counters must start at zero
+  ASRQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, kPartialOffset, st));
+  return gemv_a16(4, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, scratch, kStaticScratchBytes, sms, st,
+                  kStaticMaxSplit);
+}
+#pragma GCC visibility pop

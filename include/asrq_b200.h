@@ -84,6 +84,20 @@ int asrq_w2a16_gemv(const void* x, const uint8_t* w, const void* scales, const v
                     int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * asrq_w4a16_gemv for callers that cannot allocate device memory (a plugin that is only handed
+ * input and output buffers, a real-time callback, code running after memory pools are frozen):
+ * the scratch lives in a static device array inside the library (16 640 + 4 Mi bytes per GPU,
+ * held until exit), so there is no workspace argument and the call allocates nothing.
+ * Limits: N <= 8192 (ASRQ_ERR_LIMIT beyond).  The first call on a device looks the array's device
+ * address up (make it before any stream capture).  All calls on a device share the array; calls
+ * that overlap on the GPU race on it.  Same results as asrq_w4a16_gemv within its tolerance (the
+ * K split may differ).  No counterpart in the reference.
+ */
+int asrq_w4a16_gemv_static(const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                           const void* bias, void* y, int64_t M, int64_t N, int64_t K,
+                           int group_size, int dtype, void* stream);
+
+/*
  * Same contraction for large M (the prefill / encoder path): weights are unpacked
  * and scaled in registers, staged to shared memory and fed to tcgen05 kind::f16
  * MMAs with TMEM accumulators; activations arrive by TMA.
