@@ -1,25 +1,26 @@
 // Prefill / encoder path: y[M,N] = x[M,K] . dequant(W)[N,K]^T (+ bias) for large M.
 //
 // The weight tile is the MMA "A" operand (128 output features = 128 TMEM lanes), the
-// activation tile is the "B" operand (BT tokens = BT TMEM columns, BT <= 256 chosen
-// by the host).  One persistent block per SM, eighteen warps:
+// activation tile is the "B" operand (BT tokens = BT TMEM columns, BT <= 256 chosen by the
+// host).  One persistent block per SM, twenty warps (see kTcDequantPos for who is who):
 //
-//   warp 0      TMA producer: per 64-wide K block, one tile of activations
+//   1 warp      TMA producer: per 64-wide K block, one tile of activations
 //               (BT x 64, 128-byte swizzle) and one tile of packed weights (128 rows).
-//   warp 1      MMA issuer: tcgen05.mma kind::f16, 4 x (128 x BT x 16) per K block,
-//               fp32 accumulators in TMEM, two accumulator buffers of 256 columns.
-//   warps 2-13  dequant, three groups of four warps; group d takes the K blocks with
-//               index % 3 == d, one weight row per thread: packed words -> fp16/bf16 in
-//               registers -> q*scale+zero -> the swizzled K-major A tile in shared memory.
-//               (One group alone is latency-bound: a single warp per scheduler cannot hide
-//               its own instruction latencies, and the MMA pipe then idles 70% of the time.)
-//   warps 14-17 epilogue: tcgen05.ld of the previous tile's accumulator, + bias,
+//   1 warp      MMA issuer: tcgen05.mma kind::f16, 4 x (128 x BT x 16) per K block, fp32
+//               accumulators in TMEM (two buffers of 256 columns).
+//   12 warps    dequant, three groups of four warps; group d takes the K blocks with
+//               index % 3 == d and owns A slot d, one weight row per thread: packed words ->
+//               fp16/bf16 in registers -> q*scale+zero -> the swizzled K-major slot in shared
+//               memory.  Three slots keep the chain "MMA of block i done -> slot free ->
+//               dequant of block i+3 -> MMA of block i+3" two MMA blocks slack.  (A variant with
+//               the A operand written to tensor memory by tcgen05.st measured the same speed but
+//               leaves room for only two slots beside 2 x 224 accumulator columns.)
+//   4 warps     epilogue: tcgen05.ld of the previous tile's accumulator, + bias,
 //               convert, store, while the next tile's main loop runs.
 //
-// Rings: full[s] (TMA landed) -> deq[a] (A slot a = K block % 3 written) -> MMA -> empty[s]
-// (TMA stage reusable) and afree[a] (A slot reusable); accf[b]/acce[b] hand the accumulator
-// buffers back and forth.
-// Every wait is bounded (tcgen05.cuh).
+// Rings: full[s] (TMA landed) -> deq[a] (A slot written) -> MMA -> empty[s] (TMA stage
+// reusable) and afree[a] (A slot reusable); accf[b]/acce[b] hand the accumulator buffers
+// back and forth.  Every wait is bounded (tcgen05.cuh).
 #include <algorithm>
 #include <cstdlib>
 
@@ -38,9 +39,17 @@ struct GemmTcParams {
 };
 
 constexpr int kTcDequantGroups = 3;
-constexpr int kTcThreads = 32 * (2 + 4 * kTcDequantGroups + 4);
+constexpr int kTcWarps = 20;
+constexpr int kTcThreads = 32 * kTcWarps;
+// Warp roles.  A warp with index w issues on scheduler w % 4.  The MMA thread's instruction stream
+// is the critical path of the kernel (every tcgen05.mma / commit / barrier poll costs it 40-100
+// cycles), so scheduler 1 hosts only warp 1 (MMA), the light TMA producer (warp 9) and the one
+// epilogue warp that must live there to read TMEM lanes 32-63 (warp 5); warps 13 and 17 idle.
+constexpr int kTcMmaWarp = 1, kTcProducerWarp = 9;
+// position of a warp among the twelve dequant warps (-1: not a dequant warp)
+__constant__ int8_t kTcDequantPos[kTcWarps] = {0, -1, -1, -1, -1, -1, 1, 2, 3, -1, 4, 5, 6, -1, 7, 8, 9, -1, 10, 11};
 constexpr int kTcMaxStages = 8;
-constexpr uint32_t kATileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
+constexpr uint32_t kATileBytes = 128 * 128;  // one dequantised A slot: 128 rows x 64 16-bit elements
 constexpr uint32_t kWSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
 
 // One 32-bit word of packed weights -> 16-bit floats in natural k order, scaled.
@@ -100,7 +109,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t xbytes = uint32_t(p.bt) * 128u;
-  // [A tile x kTcDequantGroups] [TMA stage: activations (bt x 128 B) + packed weights] x nstages
+  // [A slot x kTcDequantGroups] [TMA stage: activations (bt x 128 B) + packed weights] x nstages
   constexpr uint32_t a_ring_bytes = kTcDequantGroups * kATileBytes;
   const uint32_t stage_bytes = xbytes + kWSlotBytes;
   constexpr uint32_t wbytes = 128u * 8u * BITS;
@@ -133,7 +142,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
     tc::prefetch_tmap(&tmx);
     tc::prefetch_tmap(&tmw);
   }
-  if (warp == 1) {
+  if (warp == kTcMmaWarp) {
     tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
     tc::tmem_relinquish();
   }
@@ -149,130 +158,168 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
     if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
   };
 
-  if (warp == 0) {
+  // Ring positions are carried as (index, phase) counters: the role loops below run on one
+  // thread (or one warp per scheduler), where every integer division costs ~150 cycles of
+  // dependent latency.
+  const int dpos = kTcDequantPos[warp];
+  if (warp == kTcProducerWarp) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+        const int row_x = tt * p.bt, row_w = ft * 128;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % nst;
-          const uint32_t ph = (it / nst) & 1u;
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
           mark(0, it, 0);
           const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
           tc::mbar_arrive_expect_tx(full_bar(s), xbytes + wbytes);
-          tc::tma_load_2d(sb, &tmx, kb * 64, tt * p.bt, full_bar(s));
-          tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, ft * 128, full_bar(s));
+          tc::tma_load_2d(sb, &tmx, kb * 64, row_x, full_bar(s));
+          tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, full_bar(s));
           mark(0, it, 1);
+          if (++s == nst) { s = 0; ph ^= 1u; }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kTcMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
+    // tcgen05.mma issue is paced by execution (the queue is about one instruction deep), so the
+    // pipe starves unless the next issue follows within one MMA time (~110 cycles, ~15 dependent
+    // instructions of this lone thread).  All bookkeeping for the NEXT K block -- ring counters,
+    // barrier waits -- is therefore placed between the four issues of the current one.
     if (lane == 0) {
       const uint32_t idesc = tc::instr_desc(1u, BF16 ? 1u : 0u, 128u, uint32_t(p.bt));
-      uint32_t it = 0, tcount = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-        const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
-        if (!tc::mbar_wait(acce_bar(buf), aph ^ 1u, p.status, 2)) { ok = false; break; }
+      uint32_t it = 0, tcount = 0, ph = 0, dph = 0;
+      int s = 0, a = 0;
+      bool ok = ntiles > int(blockIdx.x);
+      if (ok) {
+        ok = tc::mbar_wait(acce_bar(0), 1u, p.status, 2) && tc::mbar_wait(deq_bar(0), 0u, p.status, 4);
         tc::fence_after_sync();
+      }
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t buf = tcount & 1u;
         const uint32_t d_tmem = tmem_base + buf * 256u;
+        const bool more_tiles = tile + int(gridDim.x) < ntiles;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % nst;
-          const uint32_t ph = (it / nst) & 1u;
-          const int a = it % kTcDequantGroups;
-          const uint32_t dph = (it / kTcDequantGroups) & 1u;
-          if (!tc::mbar_wait(full_bar(s), ph, p.status, 3) || !tc::mbar_wait(deq_bar(a), dph, p.status, 4)) {
-            ok = false;
-            break;
+          mark(1, it, 0);
+          // a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address field
+          const uint64_t da = tc::smem_desc_sw128(base + a * kATileBytes);
+          const uint64_t db = tc::smem_desc_sw128(base + a_ring_bytes + s * stage_bytes);
+          tc::mma_f16(d_tmem, da, db, idesc, uint32_t(kb != 0));
+          // next K block's ring positions
+          int s1 = s + 1, a1 = a + 1;
+          uint32_t ph1 = ph, dph1 = dph;
+          if (s1 == nst) { s1 = 0; ph1 ^= 1u; }
+          if (a1 == kTcDequantGroups) { a1 = 0; dph1 ^= 1u; }
+          const bool last_kb = kb + 1 == nkb;
+          const bool have_next = !last_kb || more_tiles;
+          tc::mma_f16(d_tmem, da + 2, db + 2, idesc, 1u);
+          tc::mma_f16(d_tmem, da + 4, db + 4, idesc, 1u);
+          // deq[a1] completing implies full[s1]: the dequant group of the next block waited for that
+          // stage's TMA before it wrote the A slot and arrived (release), and this wait acquires it
+          if (have_next) ok = tc::mbar_wait(deq_bar(a1), dph1, p.status, 4);
+          tc::mma_f16(d_tmem, da + 6, db + 6, idesc, 1u);
+          // one commit frees both the TMA stage (producer) and the A slot (dequant group waits on
+          // the empty barrier of the stage its previous block used)
+          tc::mma_commit(empty_bar(s));
+          if (last_kb) tc::mma_commit(accf_bar(buf));
+          if (have_next && last_kb && ok) {  // the next tile's accumulator buffer must have been drained
+            const uint32_t nt = tcount + 1;
+            ok = tc::mbar_wait(acce_bar(nt & 1u), ((nt >> 1) & 1u) ^ 1u, p.status, 2);
           }
           tc::fence_after_sync();
-          mark(1, it, 0);
-          const uint32_t a_addr = base + a * kATileBytes, b_addr = base + a_ring_bytes + s * stage_bytes;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc::mma_f16(d_tmem, tc::smem_desc_sw128(a_addr + 32u * k), tc::smem_desc_sw128(b_addr + 32u * k),
-                        idesc, uint32_t((kb | k) != 0));
-          tc::mma_commit(empty_bar(s));
-          tc::mma_commit(afree_bar(a));
-          mark(1, it, 1);
+          s = s1; ph = ph1; a = a1; dph = dph1;
+          if (!ok) break;
         }
-        if (ok) tc::mma_commit(accf_bar(buf));
       }
     }
-  } else if (warp < 2 + 4 * kTcDequantGroups) {
+  } else if (dpos >= 0) {
     // ------------------------------ dequant ------------------------------
-    const int t = (threadIdx.x - 64) & 127;           // weight row inside the tile
-    const uint32_t dgroup = (threadIdx.x - 64) >> 7;  // which K blocks this warp group takes
-    constexpr uint32_t NDG = kTcDequantGroups;
-    const int my_tiles = (ntiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
-    const uint32_t total = uint32_t(my_tiles) * uint32_t(nkb);
-    // scale and zero of this thread's row for flat iteration i (tile-major, then K block), packed
-    auto load_sz = [&](uint32_t i) -> uint32_t {
-      const int tile = int(blockIdx.x) + int(i / nkb) * int(gridDim.x);
-      const int kb = int(i % nkb);
-      const size_t idx = (size_t(tile % p.n_ftiles) * 128 + t) * p.groups_per_row + (kb * 64) / p.group_size;
+    const int t = (dpos & 3) * 32 + lane;  // weight row inside the tile
+    const int dgroup = dpos >> 2;          // this warp group takes K blocks dgroup, dgroup+3, ...
+    constexpr int NDG = kTcDequantGroups;
+    // position of the K block being processed and of the next one (for the scale/zero prefetch)
+    int tile = blockIdx.x, kb = dgroup;
+    while (kb >= nkb && tile < ntiles) { kb -= nkb; tile += gridDim.x; }
+    int s = dgroup % nst;
+    uint32_t ph = (dgroup / nst) & 1u, dph = 0, it = dgroup;
+    const int kbpg = p.group_size / 64;  // K blocks per weight group
+    const int ft_step = int(gridDim.x) % p.n_ftiles;
+    int ft = tile % p.n_ftiles;          // feature tile of `tile`, advanced without division
+    auto load_sz = [&](int f, int k) -> uint32_t {
+      const int gi = kbpg == 1 ? k : (kbpg == 2 ? (k >> 1) : k / kbpg);
+      const size_t idx = (size_t(f) * 128 + t) * p.groups_per_row + gi;
       return uint32_t(__half_as_ushort(__ldg(p.scales + idx))) | (uint32_t(__half_as_ushort(__ldg(p.zeros + idx))) << 16);
     };
-    constexpr int PFD = 4;  // K blocks of look-ahead for the scale/zero loads
-    uint32_t szq[PFD];
+    uint32_t sz_next = tile < ntiles ? load_sz(ft, kb) : 0u;
+    bool ok = true, first = true;
+    int s_prev = 0;
+    uint32_t ph_prev = 0;
+    while (tile < ntiles && ok) {
+      const uint32_t sz = sz_next;
+      int ntile = tile, nk = kb + NDG;
+      while (nk >= nkb && ntile < ntiles) {
+        nk -= nkb;
+        ntile += gridDim.x;
+        ft += ft_step;
+        if (ft >= p.n_ftiles) ft -= p.n_ftiles;
+      }
+      if (ntile < ntiles) sz_next = load_sz(ft, nk);  // consumed three K blocks from now
+      const __half sh = __ushort_as_half(uint16_t(sz & 0xffffu)), zh = __ushort_as_half(uint16_t(sz >> 16));
+      uint32_t s2, z2;
+      if (BF16) {
+        s2 = __float_as_uint(__half2float(sh));
+        z2 = __float_as_uint(__half2float(zh));
+      } else {
+        s2 = h2_as_u32(__half2half2(sh));
+        z2 = h2_as_u32(__half2half2(zh));
+      }
+      // this group's A slot must have been consumed by the MMAs of its previous K block: their
+      // commit arrived on the empty barrier of the stage that block used (s_prev, phase ph_prev).
+      // That barrier cannot advance a second time before this wait: its next completion needs the
+      // MMAs of a later block, which need this block's slot.
+      if ((!first && !tc::mbar_wait(empty_bar(s_prev), ph_prev, p.status, 7)) ||
+          !tc::mbar_wait(full_bar(s), ph, p.status, 5)) {
+        ok = false;
+        break;
+      }
+      first = false;
+      s_prev = s;
+      ph_prev = ph;
+      if (t == 0) mark(2, it, 0);
+      const uint4* wp = reinterpret_cast<const uint4*>(smem + a_ring_bytes + s * stage_bytes + xbytes + t * (8 * BITS));
+      uint8_t* arow = smem + dgroup * kATileBytes + t * 128;
+      constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
 #pragma unroll
-    for (int i = 0; i < PFD; ++i) szq[i] = (dgroup + NDG * i < total) ? load_sz(dgroup + NDG * i) : 0u;
-    bool ok = true;
-    for (uint32_t it0 = dgroup; it0 < total && ok; it0 += NDG * PFD) {
+      for (int v = 0; v < NV; ++v) {
+        const uint4 qv = wp[v];
+        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-      for (int u = 0; u < PFD; ++u) {
-        const uint32_t it = it0 + NDG * u;
-        if (it >= total || !ok) break;
-        const int s = it % nst;
-        const uint32_t ph = (it / nst) & 1u;
-        const uint32_t sz = szq[u];
-        if (it + NDG * PFD < total) szq[u] = load_sz(it + NDG * PFD);
-        const __half sh = __ushort_as_half(uint16_t(sz & 0xffffu)), zh = __ushort_as_half(uint16_t(sz >> 16));
-        uint32_t s2, z2;
-        if (BF16) {
-          s2 = __float_as_uint(__half2float(sh));
-          z2 = __float_as_uint(__half2float(zh));
-        } else {
-          s2 = h2_as_u32(__half2half2(sh));
-          z2 = h2_as_u32(__half2half2(zh));
-        }
-        // this group's A slot must have been consumed by the MMAs of its previous K block
-        if (!tc::mbar_wait(afree_bar(dgroup), ((it / NDG) & 1u) ^ 1u, p.status, 7) ||
-            !tc::mbar_wait(full_bar(s), ph, p.status, 5)) {
-          ok = false;
-          break;
-        }
-        if (t == 0) mark(2, it, 0);
-        const uint4* wp = reinterpret_cast<const uint4*>(smem + a_ring_bytes + s * stage_bytes + xbytes + t * (8 * BITS));
-        uint8_t* arow = smem + dgroup * kATileBytes + t * 128;
-        constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
+        for (int j = 0; j < 4; ++j) {
+          constexpr int PW = 32 / BITS / 2;  // output pairs per word: 4 or 8
+          uint32_t o[PW];
+          dequant_word<BITS, BF16>(qw[j], s2, z2, o);
 #pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          const uint4 qv = wp[v];
-          const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            constexpr int PW = 32 / BITS / 2;  // output pairs per word: 4 or 8
-            uint32_t o[PW];
-            dequant_word<BITS, BF16>(qw[j], s2, z2, o);
-#pragma unroll
-            for (int cc = 0; cc < PW / 4; ++cc) {
-              const int chunk = (v * 4 + j) * (PW / 4) + cc;  // 16-byte chunk (8 elements) in the row
-              *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) =
-                  make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
-            }
+          for (int cc = 0; cc < PW / 4; ++cc) {
+            const int chunk = (v * 4 + j) * (PW / 4) + cc;  // 16-byte chunk (8 elements) in the row
+            *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) =
+                make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
           }
         }
-        tc::fence_proxy_async_smem();
-        tc::mbar_arrive(deq_bar(dgroup));
-        if (t == 0) mark(2, it, 1);
       }
+      tc::fence_proxy_async_smem();
+      tc::mbar_arrive(deq_bar(dgroup));
+      if (t == 0) mark(2, it, 1);
+      tile = ntile;
+      kb = nk;
+      it += NDG;
+      dph ^= 1u;
+      s += NDG;
+      if (s >= nst) { s -= nst; ph ^= 1u; }
     }
-  } else {
+  } else if (warp >= 2 && warp <= 5) {
     // ------------------------------ epilogue ------------------------------
     const int qd = warp & 3;
     uint32_t tcount = 0;
@@ -284,29 +331,40 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
       if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
       tc::fence_after_sync();
-      if (threadIdx.x == kTcThreads - 128) mark(3, tcount, 0);
+      if (warp == 4 && lane == 0) mark(3, tcount, 0);
       const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
+      // one output column (token) per register: the warp's 32 lanes write 32 consecutive features
+      // (64 contiguous bytes) of that token's row; the row pointer advances by N per column
+      uint16_t* yp = p.y + size_t(tt) * p.bt * p.N + f;
+      const int rows_left = p.M - tt * p.bt;  // tokens of this tile that exist
       for (int ch = 0; ch < p.bt / 32; ++ch) {
         uint32_t r[32];
         tc::tmem_ld_32x32(taddr + ch * 32, r);
         tc::tmem_ld_wait();
-        const int t0 = tt * p.bt + ch * 32;
+        if (rows_left >= (ch + 1) * 32) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int tok = t0 + j;
-          if (tok < p.M) p.y[size_t(tok) * p.N + f] = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+          for (int j = 0; j < 32; ++j) {
+            *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+            yp += p.N;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (ch * 32 + j < rows_left) *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+            yp += p.N;
+          }
         }
       }
       tc::fence_before_sync();
       tc::mbar_arrive(acce_bar(buf));
-      if (threadIdx.x == kTcThreads - 128) mark(3, tcount, 1);
+      if (warp == 4 && lane == 0) mark(3, tcount, 1);
     }
   }
 
   __syncwarp();
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kTcMmaWarp) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, 512);
   }

@@ -114,55 +114,70 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
     if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
   };
 
+  // Ring positions are (index, phase) counters: no integer division inside the role loops.
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+        const int row_w = ft * 128, row_a = tt * p.bt;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % nst;
-          const uint32_t ph = (it / nst) & 1u;
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11)) { ok = false; break; }
           mark(0, it, 0);
           const uint32_t sb = base + s * stage_bytes;
           tc::mbar_arrive_expect_tx(full_bar(s), kW8TileBytes + bbytes);
-          tc::tma_load_2d(sb, &tmw, kb * 128, ft * 128, full_bar(s));
-          tc::tma_load_2d(sb + kW8TileBytes, &tma, kb * 128, tt * p.bt, full_bar(s));
+          tc::tma_load_2d(sb, &tmw, kb * 128, row_w, full_bar(s));
+          tc::tma_load_2d(sb + kW8TileBytes, &tma, kb * 128, row_a, full_bar(s));
           mark(0, it, 1);
+          if (++s == nst) { s = 0; ph ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
+    // tcgen05.mma issue is paced by execution (the queue is about one instruction deep): the waits
+    // and ring arithmetic for the NEXT K block are placed between the four issues of the current one
+    // so that the pipe never waits for this lone thread.
     if (lane == 0) {
       const uint32_t idesc = tc::instr_desc(2u, 1u, 128u, uint32_t(p.bt));
-      uint32_t it = 0, ac = 0;
-      bool ok = true;
+      uint32_t it = 0, ac = 0, ph = 0;
+      int s = 0, gb = 0;
+      bool ok = ntiles > int(blockIdx.x);
+      if (ok) {
+        ok = tc::mbar_wait(acce_bar(0), 1u, p.status, 12) && tc::mbar_wait(full_bar(0), 0u, p.status, 13);
+        tc::fence_after_sync();
+      }
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const bool more_tiles = tile + int(gridDim.x) < ntiles;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int gb = kb % p.blocks_per_group;
-          const uint32_t buf = ac & 1u, aph = (ac >> 1) & 1u;
-          if (gb == 0) {
-            if (!tc::mbar_wait(acce_bar(buf), aph ^ 1u, p.status, 12)) { ok = false; break; }
-            tc::fence_after_sync();
-          }
-          const int s = it % nst;
-          const uint32_t ph = (it / nst) & 1u;
-          if (!tc::mbar_wait(full_bar(s), ph, p.status, 13)) { ok = false; break; }
-          tc::fence_after_sync();
           mark(1, it, 0);
+          const uint32_t buf = ac & 1u;
           const uint32_t sb = base + s * stage_bytes;
           const uint32_t d_tmem = tmem_base + buf * 256u;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc::mma_i8(d_tmem, tc::smem_desc_sw128(sb + 32u * k), tc::smem_desc_sw128(sb + kW8TileBytes + 32u * k),
-                       idesc, uint32_t((gb | k) != 0));
+          // a K step of 32 int8 = 32 bytes = +2 in the descriptor's 16-byte address field
+          const uint64_t da = tc::smem_desc_sw128(sb), db = tc::smem_desc_sw128(sb + kW8TileBytes);
+          tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
+          int s1 = s + 1, gb1 = gb + 1;
+          uint32_t ph1 = ph;
+          if (s1 == nst) { s1 = 0; ph1 ^= 1u; }
+          const bool group_end = gb1 == p.blocks_per_group;
+          if (group_end) gb1 = 0;
+          const bool have_next = kb + 1 < nkb || more_tiles;
+          tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
+          if (have_next) ok = tc::mbar_wait(full_bar(s1), ph1, p.status, 13);
+          tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
+          tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
           tc::mma_commit(empty_bar(s));
-          mark(1, it, 1);
-          if (gb == p.blocks_per_group - 1) {
+          if (group_end) {
             tc::mma_commit(accf_bar(buf));
             ++ac;
+            if (have_next && ok)  // the next group's accumulator buffer must have been drained
+              ok = tc::mbar_wait(acce_bar(ac & 1u), ((ac >> 1) & 1u) ^ 1u, p.status, 12);
           }
+          tc::fence_after_sync();
+          s = s1; ph = ph1; gb = gb1;
+          if (!ok) break;
         }
       }
     }
