@@ -195,7 +195,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       int s = 0, a = 0;
       bool ok = ntiles > int(blockIdx.x);
       if (ok) {
-        ok = tc::mbar_wait(acce_bar(0), 1u, p.status, 2) && tc::mbar_wait(deq_bar(0), 0u, p.status, 4);
+        ok = tc::mbar_wait_spin(acce_bar(0), 1u, p.status, 2) && tc::mbar_wait_spin(deq_bar(0), 0u, p.status, 4);
         tc::fence_after_sync();
       }
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
@@ -219,7 +219,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           tc::mma_f16(d_tmem, da + 4, db + 4, idesc, 1u);
           // deq[a1] completing implies full[s1]: the dequant group of the next block waited for that
           // stage's TMA before it wrote the A slot and arrived (release), and this wait acquires it
-          if (have_next) ok = tc::mbar_wait(deq_bar(a1), dph1, p.status, 4);
+          if (have_next) ok = tc::mbar_wait_spin(deq_bar(a1), dph1, p.status, 4);
           tc::mma_f16(d_tmem, da + 6, db + 6, idesc, 1u);
           // one commit frees both the TMA stage (producer) and the A slot (dequant group waits on
           // the empty barrier of the stage its previous block used)
@@ -227,7 +227,7 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
           if (last_kb) tc::mma_commit(accf_bar(buf));
           if (have_next && last_kb && ok) {  // the next tile's accumulator buffer must have been drained
             const uint32_t nt = tcount + 1;
-            ok = tc::mbar_wait(acce_bar(nt & 1u), ((nt >> 1) & 1u) ^ 1u, p.status, 2);
+            ok = tc::mbar_wait_spin(acce_bar(nt & 1u), ((nt >> 1) & 1u) ^ 1u, p.status, 2);
           }
           tc::fence_after_sync();
           s = s1; ph = ph1; a = a1; dph = dph1;

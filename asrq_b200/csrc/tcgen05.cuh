@@ -41,6 +41,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
+// Non-suspending poll, for the one thread whose wake-up latency is on the critical path.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 
 // Every wait in these kernels is bounded: after kWaitCycles SM clocks without the
 // barrier completing, the waiter records where it gave up in the status block
@@ -48,6 +60,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // and the block tears down normally.  The host reads the block with
 // asrq_check_status.
 constexpr long long kWaitCycles = 400000000ll;  // ~0.2 s at 1.9 GHz
+
+// Same bound, polling without suspension (test_wait): lower wake-up latency, costs issue slots.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, unsigned* status, unsigned site) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitCycles) {
+      if (atomicCAS(status, 0u, 1u) == 0u) status[1] = site;
+      return false;
+    }
+  }
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned site) {
   if (mbar_try_wait(bar, parity)) return true;

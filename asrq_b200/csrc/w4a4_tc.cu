@@ -17,8 +17,8 @@
 //     add float(acc) * sW[feature, group] into fp32 registers while the next group is
 //     multiplied.  After the last group: * sA[token] + bias, convert, store.
 //
-//   warp 0      TMA producer        warp 1      MMA issuer (and TMEM owner)
-//   warps 2-13  drain + epilogue: warp w reads TMEM lanes 32*(w%4).., column third (w-2)/4.
+//   warp 0      TMA producer        warps 1, 2  MMA issuers, one per accumulator buffer (warp 1 owns TMEM)
+//   warps 4-15  drain + epilogue: warp w reads TMEM lanes 32*(w%4).., column third (w-4)/4.
 //               Three warps per scheduler: the drain (one int->float convert and one FMA per
 //               output per group) needs about as many issue slots as the MMAs need cycles, so
 //               it only keeps up if its instruction latencies are hidden.
@@ -60,7 +60,7 @@ struct W4A4TcParams {
 
 constexpr int kW4A4ColGroups = 3;
 constexpr int kW4A4DrainWarps = 4 * kW4A4ColGroups;
-constexpr int kW4A4Threads = 32 * (2 + kW4A4DrainWarps);
+constexpr int kW4A4Threads = 32 * (4 + kW4A4DrainWarps);  // producer, two MMA issuers, one idle, drain
 constexpr int kW4A4MaxStages = 8;
 constexpr uint32_t kW8TileBytes = 128 * 128;
 
@@ -135,55 +135,49 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 1) {
-    // tcgen05.mma issue is paced by execution (the queue is about one instruction deep): the waits
-    // and ring arithmetic for the NEXT K block are placed between the four issues of the current one
-    // so that the pipe never waits for this lone thread.
+  } else if (warp == 1 || warp == 2) {
+    // Two MMA issuers.  Every tcgen05.mma / commit / barrier poll costs its issuing thread tens of
+    // cycles, more when heavy ALU warps (the drain) share its scheduler, and one thread alone cannot
+    // keep the pipe fed.  The groups of a tile alternate between the two TMEM accumulator buffers,
+    // so issuer w-1 takes the groups that land in buffer w-1: the two threads never touch the same
+    // accumulator, each commit tracks only its own thread's MMAs, and shared-memory stages are
+    // consumed independently, so they need no ordering between them.
     if (lane == 0) {
+      const uint32_t me = uint32_t(warp - 1);
       const uint32_t idesc = tc::instr_desc(2u, 1u, 128u, uint32_t(p.bt));
-      uint32_t it = 0, ac = 0, ph = 0;
+      const uint32_t d_tmem = tmem_base + me * 256u;
+      uint32_t it = 0, ac = 0, ph = 0;  // K block, group and stage phase, counted over ALL groups
       int s = 0, gb = 0;
-      bool ok = ntiles > int(blockIdx.x);
-      if (ok) {
-        ok = tc::mbar_wait(acce_bar(0), 1u, p.status, 12) && tc::mbar_wait(full_bar(0), 0u, p.status, 13);
-        tc::fence_after_sync();
-      }
+      bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const bool more_tiles = tile + int(gridDim.x) < ntiles;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          mark(1, it, 0);
-          const uint32_t buf = ac & 1u;
-          const uint32_t sb = base + s * stage_bytes;
-          const uint32_t d_tmem = tmem_base + buf * 256u;
-          // a K step of 32 int8 = 32 bytes = +2 in the descriptor's 16-byte address field
-          const uint64_t da = tc::smem_desc_sw128(sb), db = tc::smem_desc_sw128(sb + kW8TileBytes);
-          tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
-          int s1 = s + 1, gb1 = gb + 1;
-          uint32_t ph1 = ph;
-          if (s1 == nst) { s1 = 0; ph1 ^= 1u; }
-          const bool group_end = gb1 == p.blocks_per_group;
-          if (group_end) gb1 = 0;
-          const bool have_next = kb + 1 < nkb || more_tiles;
-          tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
-          if (have_next) ok = tc::mbar_wait(full_bar(s1), ph1, p.status, 13);
-          tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
-          tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
-          tc::mma_commit(empty_bar(s));
-          if (group_end) {
-            tc::mma_commit(accf_bar(buf));
-            ++ac;
-            if (have_next && ok)  // the next group's accumulator buffer must have been drained
-              ok = tc::mbar_wait(acce_bar(ac & 1u), ((ac >> 1) & 1u) ^ 1u, p.status, 12);
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          if ((ac & 1u) == me) {
+            if (gb == 0) {  // fresh accumulator: its previous contents must have been drained
+              ok = tc::mbar_wait_spin(acce_bar(me), ((ac >> 1) & 1u) ^ 1u, p.status, 12);
+              if (!ok) break;
+            }
+            ok = tc::mbar_wait_spin(full_bar(s), ph, p.status, 13);
+            if (!ok) break;
+            tc::fence_after_sync();
+            mark(1, it, 0);
+            const uint32_t sb = base + s * stage_bytes;
+            // a K step of 32 int8 = 32 bytes = +2 in the descriptor's 16-byte address field
+            const uint64_t da = tc::smem_desc_sw128(sb), db = tc::smem_desc_sw128(sb + kW8TileBytes);
+            tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
+            tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
+            tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
+            tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
+            tc::mma_commit(empty_bar(s));
+            if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(me));
           }
-          tc::fence_after_sync();
-          s = s1; ph = ph1; gb = gb1;
-          if (!ok) break;
+          if (++s == nst) { s = 0; ph ^= 1u; }
+          if (++gb == p.blocks_per_group) { gb = 0; ++ac; }
         }
       }
     }
-  } else {
+  } else if (warp >= 4) {
     const int qd = warp & 3;           // TMEM lane quadrant this warp may read
-    const int cg = (warp - 2) >> 2;    // column group 0..2
+    const int cg = (warp - 4) >> 2;    // column group 0..2
     const int wcols = p.bt / kW4A4ColGroups;  // columns this warp drains (multiple of 16, at most 64)
     const int nch = wcols >> 4;        // 16-column chunks: 1..4
     uint32_t ac = 0;
@@ -192,9 +186,9 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
       const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
       const int f = ft * 128 + qd * 32 + lane;
       const __half* swrow = p.sw + size_t(f) * p.groups;
-      float accf[64];
+      float2 accf[32];  // running fp32 sums, two columns per register pair (packed fp32 FMA)
 #pragma unroll
-      for (int i = 0; i < 64; ++i) accf[i] = 0.f;
+      for (int i = 0; i < 32; ++i) accf[i] = make_float2(0.f, 0.f);
       const int tok0 = tt * p.bt + cg * wcols;
       __half s_next = __ldg(swrow);
       for (int gi = 0; gi < p.groups && ok; ++gi, ++ac) {
@@ -203,7 +197,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
         if (gi + 1 < p.groups) s_next = __ldg(swrow + gi + 1);
         if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 14)) { ok = false; break; }
         tc::fence_after_sync();
-        if (threadIdx.x == 64) mark(2, ac, 0);
+        if (threadIdx.x == 128) mark(2, ac, 0);
         const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u + uint32_t(cg * wcols);
         uint32_t r[2][16];
         tc::tmem_ld_32x16(taddr, r[0]);
@@ -218,17 +212,20 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
               tc::mbar_arrive(acce_bar(buf));
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int v = int(r[ch & 1][j]);
-              accf[ch * 16 + j] = fmaf(__int2float_rn(v), s, accf[ch * 16 + j]);
+            for (int j = 0; j < 8; ++j) {
+              const int v0 = int(r[ch & 1][2 * j]), v1 = int(r[ch & 1][2 * j + 1]);
+              // one fma.rn.f32x2 for two outputs: same bits as two scalar FMAs, half the issue slots
+              accf[ch * 8 + j] = __ffma2_rn(make_float2(__int2float_rn(v0), __int2float_rn(v1)), make_float2(s, s),
+                                            accf[ch * 8 + j]);
               if (DUMP) {
-                const int tok = tok0 + ch * 16 + j;
-                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = v >> 8;
+                const int tok = tok0 + ch * 16 + 2 * j;
+                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = v0 >> 8;
+                if (tok + 1 < p.M) p.acc_dump[(size_t(tok + 1) * p.N + f) * p.groups + gi] = v1 >> 8;
               }
             }
           }
         }
-        if (threadIdx.x == 64) mark(2, ac, 1);
+        if (threadIdx.x == 128) mark(2, ac, 1);
       }
       if (!ok) break;
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
@@ -238,8 +235,8 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + ch * 16 + j;
-            if (tok < p.M)
-              p.y[size_t(tok) * p.N + f] = float_to_out16(accf[ch * 16 + j] * __ldg(p.sa + tok) + bias, p.bf16);
+            const float a = (j & 1) ? accf[ch * 8 + (j >> 1)].y : accf[ch * 8 + (j >> 1)].x;
+            if (tok < p.M) p.y[size_t(tok) * p.N + f] = float_to_out16(a * __ldg(p.sa + tok) + bias, p.bf16);
           }
         }
       }
