@@ -195,19 +195,45 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
 //   phase A  lane L owns elements L*128 .. L*128+127 (index bits 0-6 private): strides 1..64;
 //   phase B  lane L owns elements o*128 + L*4 + c, o = 0..31, c = 0..3 (bits 0-1 and 7-11 private):
 //            strides 128..2048, and the four consecutive elements pack into one store.
-// A lane's private elements live in a per-warp shared-memory array of 16-byte slots,
-// slot(owner, g) = g*32 + (owner ^ g) for the four elements 4g..4g+3: conflict-free both when every
-// lane touches its own group g and when lane L reads group L of every owner (the transpose).
-// Phase A and the quantisation are ROLLED loops over small register tiles: a fully unrolled
-// version (3600 instructions of straight-line code per warp) measured 57 us for 6000 tokens with
-// "no instruction" (instruction-fetch) as its dominant stall.
+// A lane's 128 values live in registers as 64 pairs of neighbouring elements (e_2j, e_2j+1), in
+// both phases, so every butterfly except stride 1 is one packed fp32 add and one packed fp32
+// subtract (add.f32x2 / fma.f32x2) on two pairs.  The transpose goes through a per-warp
+// shared-memory array of 16-byte slots, slot(owner, g) = g*32 + (owner ^ g) for the four elements
+// 4g..4g+3: conflict-free both when every lane writes its own groups and when lane L reads group L
+// of every owner.
+// The division by sqrt(4096) = 64 is exact and is applied to the scale only: rint((v/64) / (s/64))
+// is rint(v/s) bit for bit.
+// Quantisation without a division per element: t_lo = fma(v, inv_lo, magic), t_hi = fma(v, inv_hi,
+// magic) with inv_lo < 1/s < inv_hi (2^-22 apart) bracket the exact quotient, and adding 1.5*2^23
+// rounds to nearest-even and leaves the two's-complement code in the low mantissa bits; where the
+// two agree (all but a few elements in a million) that is rint(v/s); where they differ the true
+// quotient is computed.
 constexpr int kHad4096Warps = 3;
-constexpr int kHad4096WarpBytes = 8192 + 16384;  // fp16 staging + fp32 private array
+constexpr int kHad4096WarpBytes = 8192 + 16384;  // fp16 staging + fp32 transpose array
 
-template <int OUT>
-__global__ void __launch_bounds__(kHad4096Warps * 32)
-hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, float* __restrict__ sa,
-                          int M, int bf16) {
+__device__ __forceinline__ float2 sub2(float2 a, float2 c) { return __ffma2_rn(c, make_float2(-1.f, -1.f), a); }
+
+// codes of four values as bytes b0..b3 = low byte of each t (t = magic + code)
+__device__ __forceinline__ uint32_t quant4_bytes(float2 v01, float2 v23, float2 inv_lo, float2 inv_hi, float s) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  float2 a = __ffma2_rn(v01, inv_lo, magic), b = __ffma2_rn(v23, inv_lo, magic);
+  const float2 a2 = __ffma2_rn(v01, inv_hi, magic), b2 = __ffma2_rn(v23, inv_hi, magic);
+  const uint32_t diff = (__float_as_uint(a.x) ^ __float_as_uint(a2.x)) | (__float_as_uint(a.y) ^ __float_as_uint(a2.y)) |
+                        (__float_as_uint(b.x) ^ __float_as_uint(b2.x)) | (__float_as_uint(b.y) ^ __float_as_uint(b2.y));
+  if (diff != 0) {  // an element within 4e-6 of a rounding boundary: IEEE division
+    a.x = __fadd_rn(rintf(__fdiv_rn(v01.x, s)), 12582912.f);
+    a.y = __fadd_rn(rintf(__fdiv_rn(v01.y, s)), 12582912.f);
+    b.x = __fadd_rn(rintf(__fdiv_rn(v23.x, s)), 12582912.f);
+    b.y = __fadd_rn(rintf(__fdiv_rn(v23.y, s)), 12582912.f);
+  }
+  const uint32_t p01 = prmt(__float_as_uint(a.x), __float_as_uint(a.y), 0x0040u);
+  const uint32_t p23 = prmt(__float_as_uint(b.x), __float_as_uint(b.y), 0x0040u);
+  return prmt(p01, p23, 0x5410u);
+}
+
+template <int OUT, bool BF16>
+__global__ void __launch_bounds__(kHad4096Warps * 32, 3)
+hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, float* __restrict__ sa, int M) {
   extern __shared__ uint4 smem4[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x * kHad4096Warps + warp;
@@ -223,94 +249,75 @@ hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ 
     stg[owner * 16 + (j ^ (owner & 15))] = __ldg(src + u);
   }
   __syncwarp();
-  // phase A1: strides 1, 2, 4, 8 on blocks of 16 elements
-#pragma unroll 1
-  for (int b = 0; b < 8; ++b) {
-    float v[16];
+  // phase A: 64 pairs (e_2j, e_2j+1) of this lane's 128 consecutive elements
+  float2 P[64];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint4 u = stg[lane * 16 + ((2 * b + h) ^ (lane & 15))];
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  for (int u = 0; u < 16; ++u) {
+    const uint4 q = stg[lane * 16 + (u ^ (lane & 15))];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[8 * h + 2 * e] = in16_to_float(uint16_t(w[e] & 0xffffu), bf16);
-        v[8 * h + 2 * e + 1] = in16_to_float(uint16_t(w[e] >> 16), bf16);
+    for (int e = 0; e < 4; ++e)
+      P[4 * u + e] = BF16 ? make_float2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u))
+                          : __half22float2(u32_as_h2(w[e]));
+  }
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {  // stride 1: inside the pair
+    const float a = P[j].x, c = P[j].y;
+    P[j] = make_float2(a + c, a - c);
+  }
+#pragma unroll
+  for (int h = 1; h < 64; h <<= 1)  // strides 2..64: pair j with pair j + h
+#pragma unroll
+    for (int j = 0; j < 64; ++j)
+      if ((j & h) == 0) {
+        const float2 a = P[j], c = P[j + h];
+        P[j] = __fadd2_rn(a, c);
+        P[j + h] = sub2(a, c);
       }
-    }
 #pragma unroll
-    for (int h = 1; h < 16; h <<= 1)
-#pragma unroll
-      for (int j = 0; j < 16; ++j)
-        if ((j & h) == 0) {
-          const float a = v[j], c = v[j + h];
-          v[j] = a + c;
-          v[j + h] = a - c;
-        }
-#pragma unroll
-    for (int gq = 0; gq < 4; ++gq) {
-      const int g = 4 * b + gq;
-      pv[g * 32 + (lane ^ g)] = make_float4(v[4 * gq], v[4 * gq + 1], v[4 * gq + 2], v[4 * gq + 3]);
-    }
-  }
-  // phase A2: strides 16, 32, 64 = bits 2, 3, 4 of the group index g
-#pragma unroll 1
-  for (int gl = 0; gl < 4; ++gl) {
-    float4 w[8];
-#pragma unroll
-    for (int m = 0; m < 8; ++m) w[m] = pv[(gl + 4 * m) * 32 + (lane ^ (gl + 4 * m))];
-#pragma unroll
-    for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-      for (int m = 0; m < 8; ++m)
-        if ((m & h) == 0) {
-          const float4 a = w[m], c = w[m + h];
-          w[m] = make_float4(a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w);
-          w[m + h] = make_float4(a.x - c.x, a.y - c.y, a.z - c.z, a.w - c.w);
-        }
-#pragma unroll
-    for (int m = 0; m < 8; ++m) pv[(gl + 4 * m) * 32 + (lane ^ (gl + 4 * m))] = w[m];
-  }
+  for (int g = 0; g < 32; ++g) pv[g * 32 + (lane ^ g)] = make_float4(P[2 * g].x, P[2 * g].y, P[2 * g + 1].x, P[2 * g + 1].y);
   __syncwarp();
-  // phase B: transpose (lane L takes group L of every owner o), strides 128..2048 over o, in registers
-  float4 z[32];
-#pragma unroll
-  for (int o = 0; o < 32; ++o) z[o] = pv[lane * 32 + (o ^ lane)];
-#pragma unroll
-  for (int h = 1; h < 32; h <<= 1)
-#pragma unroll
-    for (int o = 0; o < 32; ++o)
-      if ((o & h) == 0) {
-        const float4 a = z[o], c = z[o + h];
-        z[o] = make_float4(a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w);
-        z[o + h] = make_float4(a.x - c.x, a.y - c.y, a.z - c.z, a.w - c.w);
-      }
-  float amax = 0.f;
-  __syncwarp();  // every lane has read the transposed view before the slots are reused below
+  // phase B: transpose (lane L takes group L of every owner o), strides 128..2048 over o
 #pragma unroll
   for (int o = 0; o < 32; ++o) {
-    // / sqrt(4096): exact, same bits as the division
-    z[o] = make_float4(z[o].x * 0.015625f, z[o].y * 0.015625f, z[o].z * 0.015625f, z[o].w * 0.015625f);
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(z[o].x), fabsf(z[o].y)), fmaxf(fabsf(z[o].z), fabsf(z[o].w))));
-    pv[o * 32 + lane] = z[o];  // lane-private, conflict-free: parked for the rolled quantisation loop
+    const float4 z = pv[lane * 32 + (o ^ lane)];
+    P[2 * o] = make_float2(z.x, z.y);
+    P[2 * o + 1] = make_float2(z.z, z.w);
   }
 #pragma unroll
+  for (int h = 2; h < 64; h <<= 1)
+#pragma unroll
+    for (int j = 0; j < 64; ++j)
+      if ((j & h) == 0) {
+        const float2 a = P[j], c = P[j + h];
+        P[j] = __fadd2_rn(a, c);
+        P[j + h] = sub2(a, c);
+      }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) amax = fmaxf(amax, fmaxf(fabsf(P[j].x), fabsf(P[j].y)));
+#pragma unroll
   for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
-  const QScale s = make_qscale(amax);
-  if (lane == 0) sa[token] = s.s;
+  // scale of the unnormalised values; the token's scale is that / 64 (exact)
+  float s = __fdiv_rn(amax, 7.f);
+  const bool zero = s == 0.f;
+  if (lane == 0) sa[token] = zero ? 1e-3f : s * 0.015625f;
+  if (zero) s = 1.f;  // every value is 0: any scale gives code 0
+  const float inv = __fdiv_rn(1.f, s);
+  const float il = inv * (1.f - 2.384185791015625e-07f), ih = inv * (1.f + 2.384185791015625e-07f);  // 2^-22
+  const float2 inv_lo = make_float2(il, il), inv_hi = make_float2(ih, ih);
   // element index of (o, lane, c) is o*128 + lane*4 + c: one 32-bit (int8) or 16-bit (packed) store per o
   uint32_t* d8 = reinterpret_cast<uint32_t*>(qa + size_t(token) * 4096);
   uint16_t* d4 = reinterpret_cast<uint16_t*>(qa + size_t(token) * 2048);
-#pragma unroll 4
-  for (int o = 0; o < 32; ++o) {
-    const float4 f = pv[o * 32 + lane];
-    const float v4[4] = {f.x, f.y, f.z, f.w};
-    if (OUT == 1) {
-      d8[o * 32 + lane] = pack4_int8x16(v4, s);
-    } else {
-      uint32_t w = 0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) w |= (uint32_t(quant1(v4[c], s)) & 0xFu) << (4 * c);
-      d4[o * 32 + lane] = uint16_t(w);
+  for (int o = 0; o < 32; ++o) {
+    const uint32_t b = quant4_bytes(P[2 * o], P[2 * o + 1], inv_lo, inv_hi, s);
+    if (OUT == 1) {
+      d8[o * 32 + lane] = (b << 4) & 0xf0f0f0f0u;
+    } else {
+      const uint32_t n = b & 0x0f0f0f0fu;  // four nibbles in four bytes -> 16 bits, element 0 lowest
+      const uint32_t m = n | (n >> 4);     // bytes 0 and 2 now hold two nibbles each
+      d4[o * 32 + lane] = uint16_t((m & 0xffu) | ((m >> 8) & 0xff00u));
     }
   }
 }
@@ -331,9 +338,9 @@ static int launch_quant(const uint16_t* xp, uint8_t* qa, float* sa, int64_t M, i
       case 2048: hadamard_quant_kernel<64, OUT><<<blocks, thr, 0, stream>>>(xp, qa, sa, int(M), int(K), bf16); break;
       case 4096: {
         const int smem = kHad4096Warps * kHad4096WarpBytes;
-        ASRQ_CUDA_TRY(cudaFuncSetAttribute(hadamard4096_quant_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        hadamard4096_quant_kernel<OUT><<<int((M + kHad4096Warps - 1) / kHad4096Warps), kHad4096Warps * 32, smem, stream>>>(
-            xp, qa, sa, int(M), bf16);
+        auto kern = bf16 ? hadamard4096_quant_kernel<OUT, true> : hadamard4096_quant_kernel<OUT, false>;
+        ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<int((M + kHad4096Warps - 1) / kHad4096Warps), kHad4096Warps * 32, smem, stream>>>(xp, qa, sa, int(M));
         break;
       }
       default:
