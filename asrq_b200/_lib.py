@@ -57,8 +57,12 @@ SIGNATURES = {
     "asrq_w4a4_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "asrq_w4a4_prepare_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "asrq_w4a4_prepare_weight_f8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "asrq_hadamard_quant_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
     "asrq_w4a4_gemm_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "asrq_hadamard_quant_f8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "asrq_w4a4_gemm_f8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "asrq_check_status": (c_int, [c_void_p, c_void_p]),
     "asrq_device_info_query": (c_int, [c_int, ctypes.POINTER(DeviceInfo)]),

@@ -11,6 +11,8 @@
 //
 // Quantisation: s = absmax/7 (0 -> 1e-3), q = rint(v/s) with IEEE division and
 // round-half-even, packed two's-complement nibbles, even k in the low nibble.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace asrq {
@@ -65,6 +67,19 @@ __device__ __forceinline__ uint32_t pack4_int8x16(const float* v, QScale s) {
 }
 
 // OUT = 0: packed nibbles (K/2 bytes per token); OUT = 1: int8 holding 16*q (K bytes per token).
+// Four codes as FP8 e4m3 bytes holding the value itself (the operand format of the kind::f8f6f4 GEMM).
+__device__ __forceinline__ uint32_t e4m3x2(float a, float b) {
+  return uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ uint32_t pack4_e4m3(const float* v, QScale s) {
+  return e4m3x2(float(quant1(v[0], s)), float(quant1(v[1], s))) |
+         (e4m3x2(float(quant1(v[2], s)), float(quant1(v[3], s))) << 16);
+}
+template <int OUT>
+__device__ __forceinline__ uint32_t pack4_operand(const float* v, QScale s) {
+  return OUT == 2 ? pack4_e4m3(v, s) : pack4_int8x16(v, s);
+}
+
 template <int V, int OUT>
 __global__ void __launch_bounds__(kQuantWarps * 32)
 hadamard_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa,
@@ -117,16 +132,16 @@ hadamard_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa,
   for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
   const QScale s = make_qscale(amax);
   if (lane == 0) sa[token] = s.s;
-  if (OUT == 1) {
+  if (OUT >= 1) {
     uint32_t* d8 = reinterpret_cast<uint32_t*>(qa + size_t(token) * K + lane * V);
     if (V >= 16) {
 #pragma unroll
       for (int i = 0; i < V / 16; ++i)
-        reinterpret_cast<uint4*>(d8)[i] = make_uint4(pack4_int8x16(v + 16 * i, s), pack4_int8x16(v + 16 * i + 4, s),
-                                                     pack4_int8x16(v + 16 * i + 8, s), pack4_int8x16(v + 16 * i + 12, s));
+        reinterpret_cast<uint4*>(d8)[i] = make_uint4(pack4_operand<OUT>(v + 16 * i, s), pack4_operand<OUT>(v + 16 * i + 4, s),
+                                                     pack4_operand<OUT>(v + 16 * i + 8, s), pack4_operand<OUT>(v + 16 * i + 12, s));
     } else {
 #pragma unroll
-      for (int i = 0; i < V / 4; ++i) d8[i] = pack4_int8x16(v + 4 * i, s);
+      for (int i = 0; i < V / 4; ++i) d8[i] = pack4_operand<OUT>(v + 4 * i, s);
     }
     return;
   }
@@ -172,7 +187,7 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
   for (int mask = 16; mask > 0; mask >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
   const QScale s = make_qscale(amax);
   if (lane == 0) sa[token] = s.s;
-  uint32_t* dst = reinterpret_cast<uint32_t*>(qa + size_t(token) * (OUT == 1 ? K : K / 2));
+  uint32_t* dst = reinterpret_cast<uint32_t*>(qa + size_t(token) * (OUT >= 1 ? K : K / 2));
   for (int i = lane; i < units; i += 32) {
     const uint4 u = __ldg(src + i);
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -182,8 +197,8 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
       v[2 * j] = in16_to_float(uint16_t(w[j] & 0xffffu), bf16);
       v[2 * j + 1] = in16_to_float(uint16_t(w[j] >> 16), bf16);
     }
-    if (OUT == 1) {
-      reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack4_int8x16(v, s), pack4_int8x16(v + 4, s));
+    if (OUT >= 1) {
+      reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack4_operand<OUT>(v, s), pack4_operand<OUT>(v + 4, s));
     } else {
       dst[i] = pack8_int4(v, s);
     }
@@ -213,7 +228,8 @@ constexpr int kHad4096WarpBytes = 8192 + 16384;  // fp16 staging + fp32 transpos
 
 __device__ __forceinline__ float2 sub2(float2 a, float2 c) { return __ffma2_rn(c, make_float2(-1.f, -1.f), a); }
 
-// codes of four values as bytes b0..b3 = low byte of each t (t = magic + code)
+// codes of four values: OUT 0 and 1 as bytes b0..b3 = low byte of each t (t = magic + code), OUT 2 as e4m3 bytes
+template <int OUT>
 __device__ __forceinline__ uint32_t quant4_bytes(float2 v01, float2 v23, float2 inv_lo, float2 inv_hi, float s) {
   const float2 magic = make_float2(12582912.f, 12582912.f);
   float2 a = __ffma2_rn(v01, inv_lo, magic), b = __ffma2_rn(v23, inv_lo, magic);
@@ -225,6 +241,12 @@ __device__ __forceinline__ uint32_t quant4_bytes(float2 v01, float2 v23, float2 
     a.y = __fadd_rn(rintf(__fdiv_rn(v01.y, s)), 12582912.f);
     b.x = __fadd_rn(rintf(__fdiv_rn(v23.x, s)), 12582912.f);
     b.y = __fadd_rn(rintf(__fdiv_rn(v23.y, s)), 12582912.f);
+  }
+  if (OUT == 2) {
+    const float2 nm = make_float2(-12582912.f, -12582912.f);
+    a = __fadd2_rn(a, nm);  // exact: the code as a float
+    b = __fadd2_rn(b, nm);
+    return e4m3x2(a.x, a.y) | (e4m3x2(b.x, b.y) << 16);
   }
   const uint32_t p01 = prmt(__float_as_uint(a.x), __float_as_uint(a.y), 0x0040u);
   const uint32_t p23 = prmt(__float_as_uint(b.x), __float_as_uint(b.y), 0x0040u);
@@ -311,8 +333,10 @@ hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ 
   uint16_t* d4 = reinterpret_cast<uint16_t*>(qa + size_t(token) * 2048);
 #pragma unroll
   for (int o = 0; o < 32; ++o) {
-    const uint32_t b = quant4_bytes(P[2 * o], P[2 * o + 1], inv_lo, inv_hi, s);
-    if (OUT == 1) {
+    const uint32_t b = quant4_bytes<OUT>(P[2 * o], P[2 * o + 1], inv_lo, inv_hi, s);
+    if (OUT == 2) {
+      d8[o * 32 + lane] = b;
+    } else if (OUT == 1) {
       d8[o * 32 + lane] = (b << 4) & 0xf0f0f0f0u;
     } else {
       const uint32_t n = b & 0x0f0f0f0fu;  // four nibbles in four bytes -> 16 bits, element 0 lowest
@@ -352,14 +376,15 @@ static int launch_quant(const uint16_t* xp, uint8_t* qa, float* sa, int64_t M, i
   return ASRQ_OK;
 }
 
-// out_int8 = 0: qa receives packed nibbles (M x K/2); 1: int8 holding 16*q (M x K).
+// out_fmt = 0: qa receives packed nibbles (M x K/2); 1: int8 holding 16*q (M x K); 2: e4m3 holding q (M x K).
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
-                        int out_int8, cudaStream_t stream) {
+                        int out_fmt, cudaStream_t stream) {
   if (M <= 0) return ASRQ_OK;
   const uint16_t* xp = static_cast<const uint16_t*>(x);
   const int bf16 = dtype == ASRQ_BF16;
-  return out_int8 ? launch_quant<1>(xp, qa, sa, M, K, hadamard, bf16, stream)
-                  : launch_quant<0>(xp, qa, sa, M, K, hadamard, bf16, stream);
+  if (out_fmt == 2) return launch_quant<2>(xp, qa, sa, M, K, hadamard, bf16, stream);
+  return out_fmt ? launch_quant<1>(xp, qa, sa, M, K, hadamard, bf16, stream)
+                 : launch_quant<0>(xp, qa, sa, M, K, hadamard, bf16, stream);
 }
 
 }  // namespace asrq

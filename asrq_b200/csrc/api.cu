@@ -30,10 +30,10 @@ int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const vo
                  int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
                  size_t workspace_bytes, int sm_count, cudaStream_t stream);
 bool w4a4_gemm_tc_supports(int64_t M, int64_t N, int64_t K, int group_size);
-int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int sm_count, cudaStream_t stream);
+int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int fmt, int sm_count, cudaStream_t stream);
 int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const void* sw, const void* bias, void* y,
-                   int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                   size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                   int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, int fmt,
+                   void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
 size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 // ---- errors -----------------------------------------------------------------------------
@@ -290,51 +290,79 @@ int asrq_w4a4_linear(const void* x, const uint8_t* qw, const void* sw, const voi
                         f->sm_count, static_cast<cudaStream_t>(stream));
 }
 
-int asrq_w4a4_prepare_weight(const uint8_t* qw, uint8_t* w8, int64_t N, int64_t K, void* stream) {
+// fmt: 1 = int8 holding 16x the code (kind::i8), 2 = e4m3 holding the code (kind::f8f6f4)
+static int prepare_weight(const char* who, const uint8_t* qw, uint8_t* w8, int64_t N, int64_t K, int fmt, void* stream) {
   last_error().clear();
-  if (!qw || !w8) return fail(ASRQ_ERR_NULL, "asrq_w4a4_prepare_weight: qw and w8 must not be NULL");
-  if (N <= 0 || K <= 0 || (N * K) % 32) return fail(ASRQ_ERR_SHAPE, "asrq_w4a4_prepare_weight: N*K must be a positive multiple of 32");
-  if (!aligned16(qw) || !aligned16(w8)) return fail(ASRQ_ERR_ALIGN, "asrq_w4a4_prepare_weight: qw and w8 must be 16-byte aligned");
+  if (!qw || !w8) return fail(ASRQ_ERR_NULL, "%s: qw and w8 must not be NULL", who);
+  if (N <= 0 || K <= 0 || (N * K) % 32) return fail(ASRQ_ERR_SHAPE, "%s: N*K must be a positive multiple of 32", who);
+  if (!aligned16(qw) || !aligned16(w8)) return fail(ASRQ_ERR_ALIGN, "%s: qw and w8 must be 16-byte aligned", who);
   const DeviceFacts* f;
   int rc;
   if ((rc = device_facts(&f))) return rc;
-  return expand_int4(qw, w8, size_t(N) * size_t(K), f->sm_count, static_cast<cudaStream_t>(stream));
+  return expand_int4(qw, w8, size_t(N) * size_t(K), fmt, f->sm_count, static_cast<cudaStream_t>(stream));
 }
 
-int asrq_hadamard_quant_int8(const void* x, uint8_t* a8, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
-                             void* stream) {
+static int quant_operand(const char* who, const void* x, uint8_t* a8, float* sa, int64_t M, int64_t K, int hadamard,
+                         int dtype, int fmt, void* stream) {
   last_error().clear();
-  if (!x || !a8 || !sa) return fail(ASRQ_ERR_NULL, "asrq_hadamard_quant_int8: x, a8 and sa must not be NULL");
-  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_hadamard_quant_int8: dtype %d", dtype);
-  if (M < 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "asrq_hadamard_quant_int8: M=%lld K=%lld", (long long)M, (long long)K);
-  if (!aligned16(x) || !aligned16(a8)) return fail(ASRQ_ERR_ALIGN, "asrq_hadamard_quant_int8: x and a8 must be 16-byte aligned");
+  if (!x || !a8 || !sa) return fail(ASRQ_ERR_NULL, "%s: x, a8 and sa must not be NULL", who);
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "%s: dtype %d", who, dtype);
+  if (M < 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "%s: M=%lld K=%lld", who, (long long)M, (long long)K);
+  if (!aligned16(x) || !aligned16(a8)) return fail(ASRQ_ERR_ALIGN, "%s: x and a8 must be 16-byte aligned", who);
   const DeviceFacts* f;
   int rc;
   if ((rc = device_facts(&f))) return rc;
-  return hadamard_quant_int4(x, a8, sa, M, K, hadamard, dtype, 1, static_cast<cudaStream_t>(stream));
+  return hadamard_quant_int4(x, a8, sa, M, K, hadamard, dtype, fmt, static_cast<cudaStream_t>(stream));
 }
 
-int asrq_w4a4_gemm_int8(const uint8_t* a8, const float* sa, const uint8_t* w8, const void* sw, const void* bias,
-                        void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
-                        void* workspace, size_t workspace_bytes, void* stream) {
+static int gemm_operand(const char* who, const uint8_t* a8, const float* sa, const uint8_t* w8, const void* sw,
+                        const void* bias, void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size,
+                        int dtype, int fmt, void* workspace, size_t workspace_bytes, void* stream) {
   last_error().clear();
-  if (!a8 || !sa || !w8 || !sw || !y) return fail(ASRQ_ERR_NULL, "asrq_w4a4_gemm_int8: a8, sa, w8, sw and y must not be NULL");
-  if (!workspace || workspace_bytes < kStatusBytes) return fail(ASRQ_ERR_WORKSPACE, "asrq_w4a4_gemm_int8: workspace");
-  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_w4a4_gemm_int8: dtype %d", dtype);
-  if (M < 0 || N <= 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "asrq_w4a4_gemm_int8: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (!a8 || !sa || !w8 || !sw || !y) return fail(ASRQ_ERR_NULL, "%s: a8, sa, w8, sw and y must not be NULL", who);
+  if (!workspace || workspace_bytes < kStatusBytes) return fail(ASRQ_ERR_WORKSPACE, "%s: workspace", who);
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "%s: dtype %d", who, dtype);
+  if (M < 0 || N <= 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "%s: M=%lld N=%lld K=%lld", who, (long long)M, (long long)N, (long long)K);
   if (!aligned16(a8) || !aligned16(w8) || !aligned16(y) || !aligned16(workspace))
-    return fail(ASRQ_ERR_ALIGN, "asrq_w4a4_gemm_int8: a8, w8, y and workspace must be 16-byte aligned");
+    return fail(ASRQ_ERR_ALIGN, "%s: a8, w8, y and workspace must be 16-byte aligned", who);
   if (!w4a4_gemm_tc_supports(std::max<int64_t>(M, 64), N, K, group_size))
     return fail(ASRQ_ERR_SHAPE,
-                "asrq_w4a4_gemm_int8: need N%%128==0, K%%128==0, group_size%%128==0, K%%group_size==0 "
-                "(N=%lld K=%lld g=%d)", (long long)N, (long long)K, group_size);
-  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "asrq_w4a4_gemm_int8: size");
+                "%s: need N%%128==0, K%%128==0, group_size%%128==0, K%%group_size==0 "
+                "(N=%lld K=%lld g=%d)", who, (long long)N, (long long)K, group_size);
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "%s: size", who);
   const DeviceFacts* f;
   int rc;
   if ((rc = device_facts(&f))) return rc;
   if (M == 0) return ASRQ_OK;
-  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, workspace_bytes,
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, fmt, workspace, workspace_bytes,
                         f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_w4a4_prepare_weight(const uint8_t* qw, uint8_t* w8, int64_t N, int64_t K, void* stream) {
+  return prepare_weight("asrq_w4a4_prepare_weight", qw, w8, N, K, 1, stream);
+}
+int asrq_w4a4_prepare_weight_f8(const uint8_t* qw, uint8_t* w8, int64_t N, int64_t K, void* stream) {
+  return prepare_weight("asrq_w4a4_prepare_weight_f8", qw, w8, N, K, 2, stream);
+}
+int asrq_hadamard_quant_int8(const void* x, uint8_t* a8, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
+                             void* stream) {
+  return quant_operand("asrq_hadamard_quant_int8", x, a8, sa, M, K, hadamard, dtype, 1, stream);
+}
+int asrq_hadamard_quant_f8(const void* x, uint8_t* a8, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
+                           void* stream) {
+  return quant_operand("asrq_hadamard_quant_f8", x, a8, sa, M, K, hadamard, dtype, 2, stream);
+}
+int asrq_w4a4_gemm_int8(const uint8_t* a8, const float* sa, const uint8_t* w8, const void* sw, const void* bias,
+                        void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_operand("asrq_w4a4_gemm_int8", a8, sa, w8, sw, bias, y, acc_dump, M, N, K, group_size, dtype, 1,
+                      workspace, workspace_bytes, stream);
+}
+int asrq_w4a4_gemm_f8(const uint8_t* a8, const float* sa, const uint8_t* w8, const void* sw, const void* bias,
+                      void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_operand("asrq_w4a4_gemm_f8", a8, sa, w8, sw, bias, y, acc_dump, M, N, K, group_size, dtype, 2,
+                      workspace, workspace_bytes, stream);
 }
 
 int asrq_check_status(void* workspace, void* stream) {

@@ -139,7 +139,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 }
 
 // Instruction descriptor.  D format: 1 = f32, 2 = s32.  A/B format for kind::f16:
-// 0 = f16, 1 = bf16; for kind::i8: 0 = u8, 1 = s8.  Both operands K-major.
+// 0 = f16, 1 = bf16; for kind::i8: 0 = u8, 1 = s8; for kind::f8f6f4: 0 = e4m3, 1 = e5m2.  Both operands K-major.
 __device__ __forceinline__ uint32_t instr_desc(uint32_t dfmt, uint32_t abfmt, uint32_t m, uint32_t n) {
   return (dfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
@@ -158,6 +158,16 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// kind::f8f6f4 with 8-bit operands (instruction descriptor A/B format 0 = e4m3, 1 = e5m2), f32 accumulation;
+// K = 32 per instruction like kind::i8.
+__device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }

@@ -47,6 +47,36 @@ expand_int4_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_
   }
 }
 
+// Packed signed nibbles -> one FP8 (e4m3) byte per code, natural k order.  -8..7 are exact in e4m3
+// (1 = 0x38, 2 = 0x40, 3 = 0x44, 4 = 0x48, 5 = 0x4a, 6 = 0x4c, 7 = 0x4e, 8 = 0x50, sign = 0x80).
+__device__ __forceinline__ uint32_t e4m3_of_nibble(uint32_t c) {  // c = two's-complement nibble 0..15
+  const uint32_t neg = c >> 3, mag = neg ? 16u - c : c;           // magnitude 0..8
+  // 0, 1, 2, 3 | 4, 5, 6, 7 | 8 as bytes of two table words and a constant
+  const uint32_t lo = 0x44403800u, hi = 0x4e4c4a48u;
+  const uint32_t e = mag == 8u ? 0x50u : (((mag & 4u) ? hi : lo) >> (8u * (mag & 3u))) & 0xffu;
+  return e | (neg << 7);
+}
+__global__ void __launch_bounds__(256)
+expand_int4_f8_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n_vec) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+    const uint4 q = __ldg(src + i);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r |= e4m3_of_nibble((w[j] >> (16 * h + 4 * e)) & 0xfu) << (8 * e);
+        o[2 * j + h] = r;
+      }
+    }
+    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 struct W4A4TcParams {
   const float* sa;
   const __half* sw;
@@ -55,21 +85,24 @@ struct W4A4TcParams {
   int32_t* acc_dump;
   unsigned* status;
   long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
-  int M, N, K, groups, blocks_per_group, bt, nstages, n_ftiles, n_ttiles, bf16;
+  int M, N, K, groups, blocks_per_group, bt, nbuf, nstages, n_ftiles, n_ttiles, bf16;
 };
 
-constexpr int kW4A4ColGroups = 3;
-constexpr int kW4A4DrainWarps = 4 * kW4A4ColGroups;
-constexpr int kW4A4Threads = 32 * (4 + kW4A4DrainWarps);  // producer, two MMA issuers, one idle, drain
+constexpr int kW4A4MaxBufs = 4;
 constexpr int kW4A4MaxStages = 8;
+constexpr int w4a4_threads(int cg) { return 32 * (4 + 4 * cg); }  // producer, two MMA issuers, one idle, drain
 constexpr uint32_t kW8TileBytes = 128 * 128;
 
-template <bool DUMP>
-__global__ void __launch_bounds__(kW4A4Threads, 1)
+// F8 = false: operands are int8 holding 16x the code, kind::i8, int32 sums in TMEM (256x the true sum).
+// F8 = true: operands are e4m3 bytes holding the code, kind::f8f6f4, fp32 sums in TMEM: a group sum is
+// an integer of magnitude <= 128 * 64, so it is exact, and the drain needs no int->float conversion.
+// CG: column groups of the drain (4 * CG drain warps); NCH: 16-column chunks a drain warp handles at most.
+template <bool DUMP, bool F8, int CG, int NCH>
+__global__ void __launch_bounds__(w4a4_threads(CG), 1)
 w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tma,
                const W4A4TcParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kW4A4MaxStages + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kW4A4MaxStages + 2 * kW4A4MaxBufs];
   __shared__ uint32_t tmem_slot;
 
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
@@ -82,16 +115,16 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kW4A4MaxStages + s); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + b); };
-  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + 2 + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + kW4A4MaxBufs + b); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
       tc::mbar_init(full_bar(s), 1);
       tc::mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < p.nbuf; ++b) {
       tc::mbar_init(accf_bar(b), 1);
-      tc::mbar_init(acce_bar(b), 32 * kW4A4DrainWarps);
+      tc::mbar_init(acce_bar(b), 32 * 4 * CG);
     }
     tc::fence_barrier_init();
     tc::fence_proxy_async_smem();
@@ -144,16 +177,16 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
     // consumed independently, so they need no ordering between them.
     if (lane == 0) {
       const uint32_t me = uint32_t(warp - 1);
-      const uint32_t idesc = tc::instr_desc(2u, 1u, 128u, uint32_t(p.bt));
-      const uint32_t d_tmem = tmem_base + me * 256u;
+      const uint32_t idesc = F8 ? tc::instr_desc(1u, 0u, 128u, uint32_t(p.bt)) : tc::instr_desc(2u, 1u, 128u, uint32_t(p.bt));
       uint32_t it = 0, ac = 0, ph = 0;  // K block, group and stage phase, counted over ALL groups
+      uint32_t buf = 0, bph = 0;        // accumulator buffer of group ac and the parity of its use count
       int s = 0, gb = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           if ((ac & 1u) == me) {
             if (gb == 0) {  // fresh accumulator: its previous contents must have been drained
-              ok = tc::mbar_wait_spin(acce_bar(me), ((ac >> 1) & 1u) ^ 1u, p.status, 12);
+              ok = tc::mbar_wait_spin(acce_bar(buf), bph ^ 1u, p.status, 12);
               if (!ok) break;
             }
             ok = tc::mbar_wait_spin(full_bar(s), ph, p.status, 13);
@@ -161,48 +194,59 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
             tc::fence_after_sync();
             mark(1, it, 0);
             const uint32_t sb = base + s * stage_bytes;
-            // a K step of 32 int8 = 32 bytes = +2 in the descriptor's 16-byte address field
+            const uint32_t d_tmem = tmem_base + buf * uint32_t(p.bt);
+            // a K step of 32 bytes = +2 in the descriptor's 16-byte address field
             const uint64_t da = tc::smem_desc_sw128(sb), db = tc::smem_desc_sw128(sb + kW8TileBytes);
-            tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
-            tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
-            tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
-            tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
+            if (F8) {
+              tc::mma_f8(d_tmem, da, db, idesc, uint32_t(gb != 0));
+              tc::mma_f8(d_tmem, da + 2, db + 2, idesc, 1u);
+              tc::mma_f8(d_tmem, da + 4, db + 4, idesc, 1u);
+              tc::mma_f8(d_tmem, da + 6, db + 6, idesc, 1u);
+            } else {
+              tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
+              tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
+              tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
+              tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
+            }
             tc::mma_commit(empty_bar(s));
-            if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(me));
+            if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(buf));
           }
           if (++s == nst) { s = 0; ph ^= 1u; }
-          if (++gb == p.blocks_per_group) { gb = 0; ++ac; }
+          if (++gb == p.blocks_per_group) {
+            gb = 0;
+            ++ac;
+            if (++buf == uint32_t(p.nbuf)) { buf = 0; bph ^= 1u; }
+          }
         }
       }
     }
   } else if (warp >= 4) {
     const int qd = warp & 3;           // TMEM lane quadrant this warp may read
     const int cg = (warp - 4) >> 2;    // column group 0..2
-    const int wcols = p.bt / kW4A4ColGroups;  // columns this warp drains (multiple of 16, at most 64)
-    const int nch = wcols >> 4;        // 16-column chunks: 1..4
-    uint32_t ac = 0;
+    const int wcols = p.bt / CG;       // columns this warp drains (multiple of 16, at most 16 * NCH)
+    const int nch = wcols >> 4;        // 16-column chunks: 1..NCH
+    uint32_t ac = 0, buf = 0, aph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
       const int f = ft * 128 + qd * 32 + lane;
       const __half* swrow = p.sw + size_t(f) * p.groups;
-      float2 accf[32];  // running fp32 sums, two columns per register pair (packed fp32 FMA)
+      float2 accf[8 * NCH];  // running fp32 sums, two columns per register pair (packed fp32 FMA)
 #pragma unroll
-      for (int i = 0; i < 32; ++i) accf[i] = make_float2(0.f, 0.f);
+      for (int i = 0; i < 8 * NCH; ++i) accf[i] = make_float2(0.f, 0.f);
       const int tok0 = tt * p.bt + cg * wcols;
       __half s_next = __ldg(swrow);
       for (int gi = 0; gi < p.groups && ok; ++gi, ++ac) {
-        const uint32_t buf = ac & 1u, aph = (ac >> 1) & 1u;
-        const float s = __half2float(s_next) * (1.0f / 256.0f);  // operands hold 16x the codes
+        const float s = __half2float(s_next) * (F8 ? 1.0f : 1.0f / 256.0f);  // int8 operands hold 16x the codes
         if (gi + 1 < p.groups) s_next = __ldg(swrow + gi + 1);
         if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 14)) { ok = false; break; }
         tc::fence_after_sync();
         if (threadIdx.x == 128) mark(2, ac, 0);
-        const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u + uint32_t(cg * wcols);
+        const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * uint32_t(p.bt) + uint32_t(cg * wcols);
         uint32_t r[2][16];
         tc::tmem_ld_32x16(taddr, r[0]);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < NCH; ++ch) {
           if (ch < nch) {
             tc::tmem_ld_wait();
             if (ch + 1 < nch) {
@@ -213,24 +257,27 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const int v0 = int(r[ch & 1][2 * j]), v1 = int(r[ch & 1][2 * j + 1]);
+              const uint32_t u0 = r[ch & 1][2 * j], u1 = r[ch & 1][2 * j + 1];
+              const float2 g2 = F8 ? make_float2(__uint_as_float(u0), __uint_as_float(u1))
+                                   : make_float2(__int2float_rn(int(u0)), __int2float_rn(int(u1)));
               // one fma.rn.f32x2 for two outputs: same bits as two scalar FMAs, half the issue slots
-              accf[ch * 8 + j] = __ffma2_rn(make_float2(__int2float_rn(v0), __int2float_rn(v1)), make_float2(s, s),
-                                            accf[ch * 8 + j]);
+              accf[ch * 8 + j] = __ffma2_rn(g2, make_float2(s, s), accf[ch * 8 + j]);
               if (DUMP) {
                 const int tok = tok0 + ch * 16 + 2 * j;
-                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = v0 >> 8;
-                if (tok + 1 < p.M) p.acc_dump[(size_t(tok + 1) * p.N + f) * p.groups + gi] = v1 >> 8;
+                const int v0 = F8 ? __float2int_rn(g2.x) : int(u0) >> 8, v1 = F8 ? __float2int_rn(g2.y) : int(u1) >> 8;
+                if (tok < p.M) p.acc_dump[(size_t(tok) * p.N + f) * p.groups + gi] = v0;
+                if (tok + 1 < p.M) p.acc_dump[(size_t(tok + 1) * p.N + f) * p.groups + gi] = v1;
               }
             }
           }
         }
         if (threadIdx.x == 128) mark(2, ac, 1);
+        if (++buf == uint32_t(p.nbuf)) { buf = 0; aph ^= 1u; }
       }
       if (!ok) break;
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < NCH; ++ch) {
         if (ch < nch) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -252,9 +299,17 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
   }
 }
 
-// Token-tile width: a multiple of 48 (three column groups of 16-column chunks), at most 192.
-static int w4a4_pick_bt(int64_t M, int64_t N, int sm_count) {
-  int best = 48;
+// Token-tile width.  Two drain geometries: three column groups (BT a multiple of 48, up to 192, up to
+// four 16-column chunks per warp) or four (BT a multiple of 64, up to 128, two chunks per warp, 16 drain
+// warps).  The accumulator buffers fill tensor memory: min(4, 512 / BT) of them.
+struct W4A4Tile {
+  int bt, cg;
+};
+static W4A4Tile w4a4_pick_tile(int64_t M, int64_t N, int sm_count) {
+  static const int bt_env = getenv("ASRQ_B200_W4A4_BT") ? atoi(getenv("ASRQ_B200_W4A4_BT")) : 0;  // tuning knob
+  if (bt_env > 0 && bt_env <= 192 && (bt_env % 48 == 0 || bt_env % 64 == 0))
+    return {bt_env, bt_env % 48 == 0 ? 3 : 4};
+  W4A4Tile best = {48, 3};
   double best_cost = 1e30;
   const int64_t nft = N / 128;
   for (int bt = 48; bt <= 192; bt += 48) {
@@ -263,7 +318,7 @@ static int w4a4_pick_bt(int64_t M, int64_t N, int sm_count) {
     const double cost = double(rounds) * (bt + 16);
     if (cost <= best_cost) {
       best_cost = cost;
-      best = bt;
+      best = {bt, 3};
     }
   }
   return best;
@@ -278,18 +333,22 @@ size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return 1024 + size_t(N) * K + ((size_t(M) * K + 255) & ~size_t(255)) + size_t(M) * sizeof(float) + 256;
 }
 
-int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int sm_count, cudaStream_t stream) {
+// fmt: 1 = int8 holding 16x the code, 2 = e4m3 holding the code
+int expand_int4(const uint8_t* src, uint8_t* dst, size_t n_elems, int fmt, int sm_count, cudaStream_t stream) {
   const size_t nvec = n_elems / 32;
   const int blocks = int(std::max<size_t>(1, std::min<size_t>(size_t(sm_count) * 8, (nvec + 255) / 256)));
-  expand_int4_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), nvec);
+  if (fmt == 2)
+    expand_int4_f8_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), nvec);
+  else
+    expand_int4_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), nvec);
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;
 }
 
-// GEMM proper on int8 (16x) operands already in global memory.
+// GEMM proper on 8-bit operands already in global memory (fmt as in expand_int4).
 int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const void* sw, const void* bias,
-                          void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
-                          void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                   void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, int fmt,
+                   void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
   W4A4TcParams p;
   p.sa = sa;
   p.sw = static_cast<const __half*>(sw);
@@ -306,7 +365,9 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   p.K = int(K);
   p.groups = int(K / group_size);
   p.blocks_per_group = group_size / 128;
-  p.bt = w4a4_pick_bt(M, N, sm_count);
+  const W4A4Tile tile = w4a4_pick_tile(M, N, sm_count);
+  p.bt = tile.bt;
+  p.nbuf = std::min(kW4A4MaxBufs, 512 / p.bt);
   p.n_ftiles = int(N / 128);
   p.n_ttiles = int((M + p.bt - 1) / p.bt);
   p.bf16 = dtype == ASRQ_BF16;
@@ -321,13 +382,15 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   rc = make_tmap_2d(&tma, a8, 1, false, uint64_t(K), uint64_t(M), 128, uint32_t(p.bt), true);
   if (rc) return rc;
   const int grid = int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles, sm_count));
-  if (acc_dump) {
-    ASRQ_CUDA_TRY(cudaFuncSetAttribute(w4a4_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    w4a4_tc_kernel<true><<<grid, kW4A4Threads, smem, stream>>>(tmw, tma, p);
-  } else {
-    ASRQ_CUDA_TRY(cudaFuncSetAttribute(w4a4_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    w4a4_tc_kernel<false><<<grid, kW4A4Threads, smem, stream>>>(tmw, tma, p);
-  }
+  void (*kern)(const CUtensorMap, const CUtensorMap, const W4A4TcParams);
+  if (tile.cg == 3)
+    kern = fmt == 2 ? (acc_dump ? w4a4_tc_kernel<true, true, 3, 4> : w4a4_tc_kernel<false, true, 3, 4>)
+                    : (acc_dump ? w4a4_tc_kernel<true, false, 3, 4> : w4a4_tc_kernel<false, false, 3, 4>);
+  else
+    kern = fmt == 2 ? (acc_dump ? w4a4_tc_kernel<true, true, 4, 2> : w4a4_tc_kernel<false, true, 4, 2>)
+                    : (acc_dump ? w4a4_tc_kernel<true, false, 4, 2> : w4a4_tc_kernel<false, false, 4, 2>);
+  ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  kern<<<grid, w4a4_threads(tile.cg), smem, stream>>>(tmw, tma, p);
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;
 }
@@ -342,10 +405,10 @@ int w4a4_gemm_tc(const uint8_t* qa, const float* sa, const uint8_t* qw, const vo
   if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w4a4 gemm: size");
   uint8_t* w8 = static_cast<uint8_t*>(workspace) + 1024;
   uint8_t* a8 = w8 + size_t(N) * K;
-  int rc = expand_int4(qw, w8, size_t(N) * K, sm_count, stream);
+  int rc = expand_int4(qw, w8, size_t(N) * K, 1, sm_count, stream);
   if (rc) return rc;
-  if ((rc = expand_int4(qa, a8, size_t(M) * K, sm_count, stream))) return rc;
-  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, workspace, kStatusBytes, sm_count, stream);
+  if ((rc = expand_int4(qa, a8, size_t(M) * K, 1, sm_count, stream))) return rc;
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, acc_dump, M, N, K, group_size, dtype, 1, workspace, kStatusBytes, sm_count, stream);
 }
 
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
@@ -364,8 +427,8 @@ int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void*
   float* sa = reinterpret_cast<float*>(a8 + ((size_t(M) * K + 255) & ~size_t(255)));
   int rc = hadamard_quant_int4(x, a8, sa, M, K, hadamard, dtype, 1, stream);
   if (rc) return rc;
-  if ((rc = expand_int4(qw, w8, size_t(N) * K, sm_count, stream))) return rc;
-  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, nullptr, M, N, K, group_size, dtype, workspace, kStatusBytes, sm_count, stream);
+  if ((rc = expand_int4(qw, w8, size_t(N) * K, 1, sm_count, stream))) return rc;
+  return w4a4_gemm_int8(w8, a8, sa, sw, bias, y, nullptr, M, N, K, group_size, dtype, 1, workspace, kStatusBytes, sm_count, stream);
 }
 
 }  // namespace asrq

@@ -189,14 +189,25 @@ class LinearQQ(LinearQ):
         q = torch.stack((lo, hi), dim=-1).reshape(qa.shape[0], -1).to(torch.float32)
         return q, sa.reshape(-1, 1)
 
+    # 8-bit operand family of the tensor-core path: "f8" (e4m3 bytes holding the code, tcgen05 kind::f8f6f4,
+    # fp32 group sums) or "int8" (16x the code, kind::i8, int32 group sums).  Same bits out; f8 is faster.
+    operand = os.environ.get("ASRQ_B200_W4A4_OPERAND", "f8")
+
+    def _entry(self, stem: str) -> str:
+        if self.operand not in ("f8", "int8"):
+            raise ValueError(f"LinearQQ.operand must be 'f8' or 'int8', got {self.operand!r}")
+        if stem == "prepare":
+            return "asrq_w4a4_prepare_weight_f8" if self.operand == "f8" else "asrq_w4a4_prepare_weight"
+        return f"asrq_{stem}_{self.operand}"
+
     def _prepared_weight(self) -> torch.Tensor:
-        """int8 operand form of ``weight`` (16x the code, natural k order), derived on first use and
-        whenever the packed buffer is replaced or modified; not part of ``state_dict``."""
-        key = (self.weight.data_ptr(), self.weight._version, self.weight.device)
+        """8-bit operand form of ``weight`` (natural k order), derived on first use and whenever the
+        packed buffer is replaced or modified; not part of ``state_dict``."""
+        key = (self.weight.data_ptr(), self.weight._version, self.weight.device, self.operand)
         if getattr(self, "_w8_key", None) != key:
             n, k = self.out_features, self.in_features
             w8 = torch.empty((n, k), dtype=torch.uint8, device=self.weight.device)
-            _lib.call("asrq_w4a4_prepare_weight", self.weight.data_ptr(), w8.data_ptr(), n, k,
+            _lib.call(self._entry("prepare"), self.weight.data_ptr(), w8.data_ptr(), n, k,
                       torch.cuda.current_stream(self.weight.device).cuda_stream)
             self._w8, self._w8_key = w8, key
         return self._w8
@@ -207,7 +218,7 @@ class LinearQQ(LinearQ):
 
     def forward(self, input, acc_dump=None, two_call=False):
         """``two_call=True`` forces the packed-activation sequence (asrq_hadamard_quant_int4 then
-        asrq_w4a4_gemm); the default for large M is the prologue writing int8 operands directly.
+        asrq_w4a4_gemm); the default for large M is the prologue writing 8-bit operands directly.
         Both produce the same bits."""
         self._check_buffers(input)
         if input.numel() == 0:
@@ -233,9 +244,9 @@ class LinearQQ(LinearQ):
             y = torch.empty((m, n), dtype=input.dtype, device=input.device)
             ws = _workspace(input.device, _lib.STATUS_BYTES)
             stream = torch.cuda.current_stream(input.device).cuda_stream
-            _lib.call("asrq_hadamard_quant_int8", x2.data_ptr(), a8.data_ptr(), sa.data_ptr(), m, k,
+            _lib.call(self._entry("hadamard_quant"), x2.data_ptr(), a8.data_ptr(), sa.data_ptr(), m, k,
                       1 if self.hadamard else 0, dt, stream)
-            _lib.call("asrq_w4a4_gemm_int8", a8.data_ptr(), sa.data_ptr(), w8.data_ptr(), self.scales.data_ptr(),
+            _lib.call(self._entry("w4a4_gemm"), a8.data_ptr(), sa.data_ptr(), w8.data_ptr(), self.scales.data_ptr(),
                       bias, y.data_ptr(), dump, m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
         if _CHECK:
             check_status(input.device)

@@ -188,6 +188,22 @@ int asrq_w4a4_gemm_int8(const uint8_t* a8, const float* sa, const uint8_t* w8, c
                         size_t workspace_bytes, void* stream);
 
 /*
+ * The same three steps with the 8-bit operands in FP8 (e4m3) instead of int8: a byte holds the code
+ * itself (-8..7 are exact in e4m3), the GEMM is tcgen05 kind::f8f6f4 with fp32 accumulators in tensor
+ * memory.  A group sum is an integer of magnitude <= 128 * 64 and therefore exact in fp32, so results
+ * are bit-identical to the int8 path (acc_dump receives the same integers); the drain saves the
+ * int->float conversion per output per group.  Operands of the two families do not mix.
+ * No counterpart in the reference (its W4A4 declarations are integer-only, bindings.cpp:29-43).
+ */
+int asrq_w4a4_prepare_weight_f8(const uint8_t* qw, uint8_t* w8, int64_t N, int64_t K, void* stream);
+int asrq_hadamard_quant_f8(const void* x, uint8_t* a8, float* sa, int64_t M, int64_t K,
+                           int hadamard, int dtype, void* stream);
+int asrq_w4a4_gemm_f8(const uint8_t* a8, const float* sa, const uint8_t* w8, const void* sw,
+                      const void* bias, void* y, int32_t* acc_dump, int64_t M, int64_t N,
+                      int64_t K, int group_size, int dtype, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/*
  * Reads the workspace status block back (this one DOES synchronise the stream).
  * Returns ASRQ_OK, or ASRQ_ERR_TIMEOUT when a kernel's bounded wait gave up; the
  * block is cleared on return.  No reference counterpart (its kernels spin unbounded,

@@ -88,6 +88,29 @@ def test_int8_operand_output_matches_packed_codes(k, had):
     assert torch.equal(w8.cpu().view(torch.int8).to(torch.int64), w * 16)
 
 
+@pytest.mark.parametrize("k,had", [(4096, True), (512, True), (1280, False)])
+def test_f8_operand_output_matches_packed_codes(k, had):
+    """asrq_hadamard_quant_f8 writes the code itself as an e4m3 byte, the same codes as the packed entry point."""
+    gen = torch.Generator().manual_seed(k + 2)
+    x = (torch.randn(70, k, generator=gen) * 2).half()
+    qa, sa = _quant_gpu(x, had)
+    xd = x.to(DEV)
+    a8 = torch.empty(70, k, dtype=torch.uint8, device=DEV)
+    s8 = torch.empty(70, dtype=torch.float32, device=DEV)
+    _lib.call("asrq_hadamard_quant_f8", xd.data_ptr(), a8.data_ptr(), s8.data_ptr(), 70, k, int(had), _lib.F16,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    codes = O.unpack_signed_int4(qa).to(torch.float32)
+    assert torch.equal(a8.cpu().view(torch.float8_e4m3fn).to(torch.float32), codes)
+    assert torch.equal(s8.cpu(), sa)
+    w = torch.randint(-8, 8, (128, k), generator=gen)   # every code including -8
+    pw = O.pack_signed_int4(w).to(DEV)
+    w8 = torch.empty(128, k, dtype=torch.uint8, device=DEV)
+    _lib.call("asrq_w4a4_prepare_weight_f8", pw.data_ptr(), w8.data_ptr(), 128, k, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(w8.cpu().view(torch.float8_e4m3fn).to(torch.float32), w.to(torch.float32))
+
+
 def test_hadamard_rejects_bad_k():
     x = torch.zeros(4, 768, dtype=torch.float16, device=DEV)
     qa = torch.empty(4, 384, dtype=torch.uint8, device=DEV)
@@ -141,6 +164,12 @@ def test_w4a4_gemm_exact_accumulators_and_output(m, k, n, g, bias):
     assert torch.equal(y2, y)
     y3 = lq(x.to(DEV), two_call=True)
     assert torch.equal(y3, y)
+    # the other 8-bit operand family (int8 / kind::i8 when the default is f8 / kind::f8f6f4): same sums, same bits
+    lq.operand = "int8" if lq.operand == "f8" else "f8"
+    acc5 = torch.full_like(acc, -1)
+    y5 = lq(x.to(DEV), acc_dump=acc5)
+    torch.cuda.synchronize()
+    assert torch.equal(acc5.cpu(), acc_ref) and torch.equal(y5, y)
     if n % 128 == 0 and g % 128 == 0:
         xd = x.to(DEV)
         y4 = torch.empty(m, n, dtype=torch.float16, device=DEV)
