@@ -224,7 +224,7 @@ quant_int4_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, floa
 // two agree (all but a few elements in a million) that is rint(v/s); where they differ the true
 // quotient is computed.
 constexpr int kHad4096Warps = 3;
-constexpr int kHad4096WarpBytes = 8192 + 16384;  // fp16 staging + fp32 transpose array
+constexpr int kHad4096WarpBytes = 16384;  // fp32 transpose array; the fp16 staging area is overlaid on its first half
 
 __device__ __forceinline__ float2 sub2(float2 a, float2 c) { return __ffma2_rn(c, make_float2(-1.f, -1.f), a); }
 
@@ -260,8 +260,8 @@ hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x * kHad4096Warps + warp;
   if (token >= M) return;  // warp-uniform; only warp-level synchronisation below
-  uint4* stg = smem4 + warp * (kHad4096WarpBytes / 16);  // 512 slots of 8 fp16
-  float4* pv = reinterpret_cast<float4*>(stg + 512);     // 1024 slots of 4 fp32
+  uint4* stg = smem4 + warp * (kHad4096WarpBytes / 16);  // 512 slots of 8 fp16, dead once phase A has loaded them
+  float4* pv = reinterpret_cast<float4*>(stg);           // 1024 slots of 4 fp32
   // coalesced global load, each 16-byte unit handed to the lane that owns it in phase A
   const uint4* src = reinterpret_cast<const uint4*>(x + size_t(token) * 4096);
 #pragma unroll
@@ -282,6 +282,7 @@ hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ 
       P[4 * u + e] = BF16 ? make_float2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u))
                           : __half22float2(u32_as_h2(w[e]));
   }
+  __syncwarp();  // every lane has read its staging row: pv may overwrite the area
 #pragma unroll
   for (int j = 0; j < 64; ++j) {  // stride 1: inside the pair
     const float a = P[j].x, c = P[j].y;

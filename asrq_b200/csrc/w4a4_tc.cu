@@ -184,13 +184,16 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          // Both issuers observe every phase of every stage barrier, also for the other one's K blocks:
+          // a waiter that skipped a phase could mistake an older, still incomplete phase of the same
+          // parity for the one it wants.  (Accumulator buffers never change hands: their number is even.)
+          ok = tc::mbar_wait_spin(full_bar(s), ph, p.status, 13);
+          if (!ok) break;
           if ((ac & 1u) == me) {
             if (gb == 0) {  // fresh accumulator: its previous contents must have been drained
               ok = tc::mbar_wait_spin(acce_bar(buf), bph ^ 1u, p.status, 12);
               if (!ok) break;
             }
-            ok = tc::mbar_wait_spin(full_bar(s), ph, p.status, 13);
-            if (!ok) break;
             tc::fence_after_sync();
             mark(1, it, 0);
             const uint32_t sb = base + s * stage_bytes;
@@ -367,7 +370,7 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   p.blocks_per_group = group_size / 128;
   const W4A4Tile tile = w4a4_pick_tile(M, N, sm_count);
   p.bt = tile.bt;
-  p.nbuf = std::min(kW4A4MaxBufs, 512 / p.bt);
+  p.nbuf = 512 / p.bt >= 4 ? 4 : 2;  // even, so that a buffer always belongs to the same issuer
   p.n_ftiles = int(N / 128);
   p.n_ttiles = int((M + p.bt - 1) / p.bt);
   p.bf16 = dtype == ASRQ_BF16;

@@ -193,7 +193,10 @@ class W4A4Config2(Workload):
                "peak": int8_tops, "peak_source": "torch._int_mm 8192^3 timed in this run (8-bit tensor peak is not in MEASURED_PEAKS.json; "
                               "fp8 and int8 have the same nominal rate)",
                "frac": ach / int8_tops if int8_tops else None,
-               "frac_of_2x_bf16_measured": ach / (2 * peaks["bf16_tflops"]), "traffic": None}
+               "frac_of_2x_bf16_measured": ach / (2 * peaks["bf16_tflops"]),
+               # dram__bytes_read.sum + dram__bytes_write.sum of one w4a4_tc_kernel launch, from the ncu capture
+               # summarised in profiles/w4a4_prologue_and_gemm_c2.md (the 12 MB of outputs were still in L2)
+               "traffic": 28899584, "traffic_algorithmic": self.gemm_bytes()}
         pro = self.prologue_bytes() / (kernel_ms["hadamard_quant"] * 1e-3) / 1e9
         out["prologue"] = {"kernel": "hadamard4096_quant_kernel", "bound": "hbm", "achieved": pro, "unit": "GB/s",
                            "peak": peaks["hbm_gbs"], "frac": pro / peaks["hbm_gbs"], "of": peaks["source"]}
@@ -279,7 +282,9 @@ class W4A16Config1(Workload):
         ach = self.units_per_step() / (kernel_ms["gemm_a16_tc"] * 1e-3) / 1e12
         return {"kernel": "gemm_a16_tc", "bound": "tensor", "achieved": ach, "unit": "TFLOP/s",
                 "peak": peaks["bf16_tflops"], "frac": ach / peaks["bf16_tflops"], "of": peaks["source"] + " (burst)",
-                "traffic": None}
+                # dram bytes of one gemm_a16_tc_kernel launch from the ncu capture summarised in
+                # profiles/gemm_a16_tc_c1.md (x and W are L2 hits after the first touch, y was still in L2)
+                "traffic": 7364352, "traffic_algorithmic": 22691840}
 
     def cpu_sample(self):
         from oracle import linearq_oracle as O
@@ -372,7 +377,11 @@ class DecodeSweepConfig3(Workload):
     def roofline(self, kernel_ms, peaks, int8_tops):
         ach = self.total_bytes / (kernel_ms["gemv_a16 (30 launches)"] * 1e-3) / 1e9
         return {"kernel": "gemv_a16", "bound": "hbm", "achieved": ach, "unit": "GB/s", "peak": peaks["hbm_gbs"],
-                "frac": ach / peaks["hbm_gbs"], "of": peaks["source"], "traffic": None}
+                "frac": ach / peaks["hbm_gbs"], "of": peaks["source"],
+                # ncu captured one launch of the sweep (W4 2048->6144, M=1): 7 096 832 B of DRAM reads for
+                # 7 094 272 algorithmic bytes (profiles/gemv_a16_c3.md); the sweep's traffic is its algorithmic
+                # bytes scaled by that ratio (every launch streams its weights exactly once)
+                "traffic": self.total_bytes * 7096832.0 / 7094272.0}
 
     def cpu_sample(self):
         from oracle import linearq_oracle as O
