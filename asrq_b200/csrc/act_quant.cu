@@ -17,6 +17,8 @@
 
 namespace asrq {
 
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 constexpr int kQuantWarps = 4;
 
 __device__ __forceinline__ float in16_to_float(uint16_t b, bool bf16) {
@@ -364,7 +366,7 @@ static int launch_quant(const uint16_t* xp, uint8_t* qa, float* sa, int64_t M, i
       case 4096: {
         const int smem = kHad4096Warps * kHad4096WarpBytes;
         auto kern = bf16 ? hadamard4096_quant_kernel<OUT, true> : hadamard4096_quant_kernel<OUT, false>;
-        ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), size_t(smem))) return rc;
         kern<<<int((M + kHad4096Warps - 1) / kHad4096Warps), kHad4096Warps * 32, smem, stream>>>(xp, qa, sa, int(M));
         break;
       }

@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "tcgen05.cuh"
 
@@ -105,8 +106,41 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs a driver call of a few microseconds, as much as a short kernel runs; a
+// decode or prefill loop calls with the same buffers over and over, so the last maps are remembered.
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t inner, rows;
+  uint32_t box_inner, box_rows;
+  int elem_bytes, flags;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && inner == o.inner && rows == o.rows && box_inner == o.box_inner && box_rows == o.box_rows &&
+           elem_bytes == o.elem_bytes && flags == o.flags;
+  }
+};
+struct TmapEntry {
+  TmapKey key;
+  CUtensorMap map;
+  bool used = false;
+};
+constexpr int kTmapCache = 64;
+std::mutex g_tmap_mutex;
+TmapEntry g_tmap_cache[kTmapCache];
+int g_tmap_next = 0;
+}  // namespace
+
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool bf16, uint64_t inner, uint64_t rows,
                  uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+  const TmapKey key = {base, inner, rows, box_inner, box_rows, elem_bytes, (bf16 ? 1 : 0) | (swizzle128 ? 2 : 0)};
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    for (const TmapEntry& e : g_tmap_cache)
+      if (e.used && e.key == key) {
+        *out = e.map;
+        return ASRQ_OK;
+      }
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(ASRQ_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
   const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
@@ -121,6 +155,34 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool bf16, 
                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(ASRQ_ERR_SHAPE, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  TmapEntry& e = g_tmap_cache[g_tmap_next];
+  g_tmap_next = (g_tmap_next + 1) % kTmapCache;
+  e.key = key;
+  e.map = *out;
+  e.used = true;
+  return ASRQ_OK;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) and size, not once per launch.
+int ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  struct Seen {
+    const void* kernel;
+    int device;
+    size_t bytes;
+  };
+  static std::mutex mu;
+  static std::vector<Seen> seen;
+  int dev = 0;
+  ASRQ_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Seen& s : seen)
+      if (s.kernel == kernel && s.device == dev && s.bytes >= bytes) return ASRQ_OK;
+  }
+  ASRQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+  std::lock_guard<std::mutex> lock(mu);
+  seen.push_back({kernel, dev, bytes});
   return ASRQ_OK;
 }
 

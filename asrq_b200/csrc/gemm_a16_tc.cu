@@ -24,9 +24,12 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include "dequant.cuh"
 #include "tcgen05.cuh"
 
 namespace asrq {
+
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 struct GemmTcParams {
   const __half* scales;
@@ -51,51 +54,6 @@ __constant__ int8_t kTcDequantPos[kTcWarps] = {0, -1, -1, -1, -1, -1, 1, 2, 3, -
 constexpr int kTcMaxStages = 8;
 constexpr uint32_t kATileBytes = 128 * 128;  // one dequantised A slot: 128 rows x 64 16-bit elements
 constexpr uint32_t kWSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
-
-// One 32-bit word of packed weights -> 16-bit floats in natural k order, scaled.
-// out holds 32/BITS/2 packed pairs.
-template <int BITS, bool BF16>
-__device__ __forceinline__ void dequant_word(uint32_t q, uint32_t s2, uint32_t z2, uint32_t* out) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t t = prmt(q, q, 0x1111u * j);  // byte j replicated
-    if (!BF16) {
-      const uint32_t magic = 0x64006400u;  // 1024 | field
-      if (BITS == 4) {
-        const uint32_t v = lop3_and_or(t, 0x00f0000fu, magic);  // (1024+e0, 1024+16*e1)
-        const __half2 c = __hfma2(u32_as_h2(v), u32_as_h2(0x2c003c00u), u32_as_h2(0xd400e400u));
-        out[j] = h2_as_u32(__hfma2(c, u32_as_h2(s2), u32_as_h2(z2)));
-      } else {
-        const uint32_t v0 = lop3_and_or(t, 0x000c0003u, magic);  // (1024+e0, 1024+4*e1)
-        const uint32_t v1 = lop3_and_or(t, 0x00c00030u, magic);  // (1024+16*e2, 1024+64*e3)
-        const __half2 c0 = __hfma2(u32_as_h2(v0), u32_as_h2(0x34003c00u), u32_as_h2(0xdc00e400u));
-        const __half2 c1 = __hfma2(u32_as_h2(v1), u32_as_h2(0x24002c00u), u32_as_h2(0xcc00d400u));
-        out[2 * j] = h2_as_u32(__hfma2(c0, u32_as_h2(s2), u32_as_h2(z2)));
-        out[2 * j + 1] = h2_as_u32(__hfma2(c1, u32_as_h2(s2), u32_as_h2(z2)));
-      }
-    } else {
-      // bf16 activations: exact codes via the fp16 trick, q*scale+zero in fp32, one rounding to bf16
-      // (s2, z2 carry the fp32 scale and zero bit patterns in this mode).
-      const uint32_t magic = 0x64006400u;
-      const float sf = __uint_as_float(s2), zf = __uint_as_float(z2);
-      if (BITS == 4) {
-        const uint32_t v = lop3_and_or(t, 0x00f0000fu, magic);
-        const float2 c = __half22float2(__hfma2(u32_as_h2(v), u32_as_h2(0x2c003c00u), u32_as_h2(0xd400e400u)));
-        const __nv_bfloat162 w = __floats2bfloat162_rn(fmaf(c.x, sf, zf), fmaf(c.y, sf, zf));
-        out[j] = *reinterpret_cast<const uint32_t*>(&w);
-      } else {
-        const uint32_t v0 = lop3_and_or(t, 0x000c0003u, magic);
-        const uint32_t v1 = lop3_and_or(t, 0x00c00030u, magic);
-        const float2 c0 = __half22float2(__hfma2(u32_as_h2(v0), u32_as_h2(0x34003c00u), u32_as_h2(0xdc00e400u)));
-        const float2 c1 = __half22float2(__hfma2(u32_as_h2(v1), u32_as_h2(0x24002c00u), u32_as_h2(0xcc00d400u)));
-        const __nv_bfloat162 w0 = __floats2bfloat162_rn(fmaf(c0.x, sf, zf), fmaf(c0.y, sf, zf));
-        const __nv_bfloat162 w1 = __floats2bfloat162_rn(fmaf(c1.x, sf, zf), fmaf(c1.y, sf, zf));
-        out[2 * j] = *reinterpret_cast<const uint32_t*>(&w0);
-        out[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&w1);
-      }
-    }
-  }
-}
 
 template <int BITS, bool BF16>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -397,15 +355,25 @@ template <int BITS, bool BF16>
 static int launch_tc(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmTcParams& p, int grid, size_t smem,
                      cudaStream_t stream) {
   auto kern = gemm_a16_tc_kernel<BITS, BF16>;
-  ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
   kern<<<grid, kTcThreads, smem, stream>>>(tmx, tmw, p);
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;
 }
 
+bool gemm_a16_tc2_supports(int64_t M, int64_t N, int64_t K, int group_size);
+int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream);
+
 int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+  // The CTA-pair variant (gemm_a16_tc2.cu, tcgen05 cta_group::2) measured slower on the shapes tried
+  // (32.5 us against 25.2 us on M=1500 K=1280 N=5120) and runs only on request.
+  if (getenv("ASRQ_B200_TC_PAIR") && gemm_a16_tc2_supports(M, N, K, group_size))
+    return gemm_a16_tc2(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
+                        sm_count, stream);
   if (N % 128 || K % 64 || group_size <= 0 || group_size % 64 || K % group_size)
     return fail(ASRQ_ERR_SHAPE,
                 "w%da16 gemm: need N%%128==0, K%%64==0, group_size%%64==0, K%%group_size==0 "

@@ -1,0 +1,372 @@
+// Prefill / encoder path on CTA pairs: y[M,N] = x[M,K] . dequant(W)[N,K]^T (+ bias) for large M.
+//
+// Same roles as gemm_a16_tc.cu, but two CTAs of a cluster share one MMA (tcgen05 cta_group::2,
+// M = 256): CTA r of the pair dequantises feature tile 2j + r (its 128 A rows) into its own shared
+// memory and loads HALF of the activation tile (BT/2 token rows) by TMA; one thread of CTA 0 issues
+// 128x(2)xBTx16 MMAs that read A from both CTAs and B halves from both, and each CTA gets its own
+// feature tile's accumulators in its own tensor memory.  Per SM and K block that halves the
+// activation rows the TMA unit has to fetch and the number of MMA instructions to issue, which is
+// what bounds the one-CTA kernel.
+//
+// Barriers (all in shared memory, same offsets in both CTAs):
+//   wfull[s]   local    packed weights of stage s landed (this CTA's own TMA)
+//   full[s]    CTA 0    both halves of the activation tile landed (TMA of both CTAs, byte count)
+//   empty[s]   both     stage s consumed: multicast tcgen05.commit of CTA 0's issuer
+//   deq[a]     CTA 0    A slot a written in BOTH CTAs (256 arrivals, CTA 1's come over the cluster)
+//   afree[a]   both     A slot a consumed (multicast commit)
+//   accf[b]    both     accumulator buffer b complete (multicast commit)
+//   acce[b]    CTA 0    buffer b drained by both CTAs' epilogues (256 arrivals)
+// Every barrier has one consumer that sees each phase in order.  No TMA multicast.  Every wait is bounded.
+#include <algorithm>
+#include <cstdlib>
+
+#include "dequant.cuh"
+#include "tcgen05.cuh"
+
+namespace asrq {
+
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
+namespace {
+
+struct GemmTc2Params {
+  const __half* scales;
+  const __half* zeros;
+  const __half* bias;
+  uint16_t* y;
+  unsigned* status;
+  int M, N, K, group_size, groups_per_row, bt, nstages, n_fpairs, n_ttiles;
+};
+
+constexpr int kT2Groups = 3;
+constexpr int kT2Slots = 6;  // A slots: two per dequant group (slot = K-block count % 6, group = count % 3), so that a
+                             // group need not wait for the MMAs of its previous block before starting the next
+constexpr int kT2Warps = 20;
+constexpr int kT2Threads = 32 * kT2Warps;
+constexpr int kT2MmaWarp = 1, kT2ProducerWarp = 9;
+// position of a warp among the twelve dequant warps (-1: not a dequant warp); scheduler 1 (warps 1, 5,
+// 9, 13, 17) hosts no ALU-heavy warp
+__constant__ int8_t kT2DequantPos[kT2Warps] = {0, -1, -1, -1, -1, -1, 1, 2, 3, -1, 4, 5, 6, -1, 7, 8, 9, -1, 10, 11};
+constexpr int kT2MaxStages = 8;
+constexpr uint32_t kT2ATileBytes = 128 * 128;  // one dequantised A slot: 128 rows x 64 16-bit elements
+constexpr uint32_t kT2WSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
+
+template <int BITS, bool BF16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kT2Threads, 1)
+gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
+                    const GemmTc2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[3 * kT2MaxStages + 2 * kT2Slots + 4];
+  __shared__ uint32_t tmem_slot;
+
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t xbytes = uint32_t(p.bt / 2) * 128u;  // this CTA's half of the activation tile
+  constexpr uint32_t a_ring_bytes = kT2Slots * kT2ATileBytes;
+  const uint32_t stage_bytes = xbytes + kT2WSlotBytes;
+  constexpr uint32_t wbytes = 128u * 8u * BITS;
+  const int nst = p.nstages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_ctarank();  // 0: issues the MMAs and owns the shared barriers
+  const int cluster = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+  const uint32_t bar0 = tc::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kT2MaxStages + s); };
+  auto wfull_bar = [&](int s) { return bar0 + 8u * (2 * kT2MaxStages + s); };
+  auto deq_bar = [&](int a) { return bar0 + 8u * (3 * kT2MaxStages + a); };
+  auto afree_bar = [&](int a) { return bar0 + 8u * (3 * kT2MaxStages + kT2Slots + a); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 2 + b); };
+  // arrive on a barrier of CTA 0 from either CTA
+  auto arrive_on_leader = [&](uint32_t bar) {
+    if (rank == 0) {
+      tc::mbar_arrive(bar);
+    } else {
+      tc::mbar_arrive_cluster(tc::mapa(bar, 0));
+    }
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nst; ++s) {
+      tc::mbar_init(full_bar(s), 1);
+      tc::mbar_init(empty_bar(s), 1);
+      tc::mbar_init(wfull_bar(s), 1);
+    }
+    for (int a = 0; a < kT2Slots; ++a) {
+      tc::mbar_init(deq_bar(a), 256);
+      tc::mbar_init(afree_bar(a), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(accf_bar(b), 1);
+      tc::mbar_init(acce_bar(b), 256);
+    }
+    tc::fence_barrier_init();
+    tc::fence_proxy_async_smem();
+    tc::prefetch_tmap(&tmx);
+    tc::prefetch_tmap(&tmw);
+  }
+  if (warp == kT2MmaWarp) {
+    tc::tmem_alloc_pair(tc::smem_u32(&tmem_slot), 512);
+    tc::tmem_relinquish_pair();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync();  // the peer's barriers are initialised before anything arrives on them
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+
+  const int nunits = p.n_fpairs * p.n_ttiles;  // a unit: feature tiles 2j, 2j+1 of token tile tt
+  const int nkb = p.K / 64;
+  const int dpos = kT2DequantPos[warp];
+
+  if (warp == kT2ProducerWarp) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      const uint32_t full0 = tc::mapa(full_bar(0), 0);  // CTA 0's full barriers, as seen from here
+      uint32_t ph = 0;
+      int s = 0;
+      bool ok = true;
+      for (int unit = cluster; unit < nunits && ok; unit += nclusters) {
+        const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
+        const int row_x = tt * p.bt + int(rank) * (p.bt / 2), row_w = (2 * fp + int(rank)) * 128;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
+          const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
+          tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
+          tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
+          if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(s), 2u * xbytes);
+          tc::tma_load_2d_pair(sb, &tmx, kb * 64, row_x, full0 + 8u * s);
+          if (++s == nst) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == kT2MmaWarp) {
+    // ------------------------------ MMA issuer (CTA 0 only) ------------------------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = tc::instr_desc(1u, BF16 ? 1u : 0u, 256u, uint32_t(p.bt));
+      uint32_t ph = 0, dph = 0, ucount = 0;
+      int s = 0, a = 0;
+      bool ok = true;
+      for (int unit = cluster; unit < nunits && ok; unit += nclusters, ++ucount) {
+        const uint32_t buf = ucount & 1u;
+        const uint32_t d_tmem = tmem_base + buf * 256u;
+        // the accumulator buffer must have been drained by both CTAs
+        ok = tc::mbar_wait_spin(acce_bar(buf), ((ucount >> 1) & 1u) ^ 1u, p.status, 2);
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          ok = tc::mbar_wait_spin(deq_bar(a), dph, p.status, 4) && tc::mbar_wait_spin(full_bar(s), ph, p.status, 3);
+          if (!ok) break;
+          tc::fence_after_sync();
+          // a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address field
+          const uint64_t da = tc::smem_desc_sw128(base + a * kT2ATileBytes);
+          const uint64_t db = tc::smem_desc_sw128(base + a_ring_bytes + s * stage_bytes);
+          tc::mma_f16_pair(d_tmem, da, db, idesc, uint32_t(kb != 0));
+          tc::mma_f16_pair(d_tmem, da + 2, db + 2, idesc, 1u);
+          tc::mma_f16_pair(d_tmem, da + 4, db + 4, idesc, 1u);
+          tc::mma_f16_pair(d_tmem, da + 6, db + 6, idesc, 1u);
+          // frees the stage and the A slot in both CTAs
+          tc::mma_commit_pair(empty_bar(s), 3);
+          tc::mma_commit_pair(afree_bar(a), 3);
+          if (kb + 1 == nkb) tc::mma_commit_pair(accf_bar(buf), 3);
+          if (++s == nst) { s = 0; ph ^= 1u; }
+          if (++a == kT2Slots) { a = 0; dph ^= 1u; }
+        }
+      }
+    }
+  } else if (dpos >= 0) {
+    // ------------------------------ dequant (both CTAs) ------------------------------
+    const int t = (dpos & 3) * 32 + lane;  // weight row inside the tile
+    const int dgroup = dpos >> 2;          // this warp group takes K blocks dgroup, dgroup+3, ... and owns A slot dgroup
+    int unit = cluster, kb = dgroup;
+    while (kb >= nkb && unit < nunits) { kb -= nkb; unit += nclusters; }
+    int s = dgroup % nst;
+    uint32_t ph = (dgroup / nst) & 1u;
+    int a = dgroup;    // A slot of the current K block (count % kT2Slots) and the parity of its use count
+    uint32_t aph = 0;
+    const int kbpg = p.group_size / 64;  // K blocks per weight group
+    auto load_sz = [&](int u, int k) -> uint32_t {
+      const int f = 2 * (u % p.n_fpairs) + int(rank);
+      const int gi = kbpg == 1 ? k : (kbpg == 2 ? (k >> 1) : k / kbpg);
+      const size_t idx = (size_t(f) * 128 + t) * p.groups_per_row + gi;
+      return uint32_t(__half_as_ushort(__ldg(p.scales + idx))) | (uint32_t(__half_as_ushort(__ldg(p.zeros + idx))) << 16);
+    };
+    uint32_t sz_next = unit < nunits ? load_sz(unit, kb) : 0u;
+    while (unit < nunits) {
+      const uint32_t sz = sz_next;
+      int nunit = unit, nk = kb + kT2Groups;
+      while (nk >= nkb && nunit < nunits) { nk -= nkb; nunit += nclusters; }
+      if (nunit < nunits) sz_next = load_sz(nunit, nk);  // consumed three K blocks from now
+      const __half sh = __ushort_as_half(uint16_t(sz & 0xffffu)), zh = __ushort_as_half(uint16_t(sz >> 16));
+      uint32_t s2, z2;
+      if (BF16) {
+        s2 = __float_as_uint(__half2float(sh));
+        z2 = __float_as_uint(__half2float(zh));
+      } else {
+        s2 = h2_as_u32(__half2half2(sh));
+        z2 = h2_as_u32(__half2half2(zh));
+      }
+      // the A slot must have been consumed by the MMAs of the K block that used it last (six blocks ago,
+      // this group's own): their commit arrived on the slot's barrier in both CTAs
+      if (!tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7) || !tc::mbar_wait(wfull_bar(s), ph, p.status, 5)) break;
+      const uint4* wp = reinterpret_cast<const uint4*>(smem + a_ring_bytes + s * stage_bytes + xbytes + t * (8 * BITS));
+      uint8_t* arow = smem + a * kT2ATileBytes + t * 128;
+      constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const uint4 qv = wp[v];
+        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          constexpr int PW = 32 / BITS / 2;  // output pairs per word: 4 or 8
+          uint32_t o[PW];
+          dequant_word<BITS, BF16>(qw[j], s2, z2, o);
+#pragma unroll
+          for (int cc = 0; cc < PW / 4; ++cc) {
+            const int chunk = (v * 4 + j) * (PW / 4) + cc;  // 16-byte chunk (8 elements) in the row
+            *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) =
+                make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
+          }
+        }
+      }
+      tc::fence_proxy_async_smem();
+      arrive_on_leader(deq_bar(a));
+      unit = nunit;
+      kb = nk;
+      s += kT2Groups;
+      if (s >= nst) { s -= nst; ph ^= 1u; }
+      a += kT2Groups;
+      if (a >= kT2Slots) { a -= kT2Slots; aph ^= 1u; }
+    }
+  } else if (warp >= 2 && warp <= 5) {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int qd = warp & 3;
+    uint32_t ucount = 0;
+    bool ok = true;
+    for (int unit = cluster; unit < nunits && ok; unit += nclusters, ++ucount) {
+      const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
+      const uint32_t buf = ucount & 1u, aph = (ucount >> 1) & 1u;
+      const int f = (2 * fp + int(rank)) * 128 + qd * 32 + lane;
+      const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
+      if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
+      tc::fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
+      // one output column (token) per register: the warp's 32 lanes write 32 consecutive features
+      uint16_t* yp = p.y + size_t(tt) * p.bt * p.N + f;
+      const int rows_left = p.M - tt * p.bt;  // tokens of this tile that exist
+      for (int ch = 0; ch < p.bt / 32; ++ch) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(taddr + ch * 32, r);
+        tc::tmem_ld_wait();
+        if (rows_left >= (ch + 1) * 32) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+            yp += p.N;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (ch * 32 + j < rows_left) *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+            yp += p.N;
+          }
+        }
+      }
+      tc::fence_before_sync();
+      arrive_on_leader(acce_bar(buf));
+    }
+  }
+
+  __syncwarp();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its memory
+  if (warp == kT2MmaWarp) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+// Token-tile width: the multiple of 32 (<= 256, <= M) that minimises rounds over the CTA pairs x
+// (tile width + fixed per-tile overhead).
+int pick_bt(int64_t M, int64_t npairs, int nclusters) {
+  if (const char* e = getenv("ASRQ_B200_TC_BT")) {  // tuning knob: force the token-tile width
+    const int v = atoi(e);
+    if (v >= 32 && v <= 256 && v % 32 == 0) return v;
+  }
+  int best = 32;
+  double best_cost = 1e30;
+  for (int bt = 32; bt <= 256; bt += 32) {
+    if (bt > M && bt != 32) break;
+    const int64_t units = npairs * ((M + bt - 1) / bt);
+    const int64_t rounds = (units + nclusters - 1) / nclusters;
+    const double cost = double(rounds) * (bt + 24);
+    if (cost <= best_cost) {
+      best_cost = cost;
+      best = bt;
+    }
+  }
+  return best;
+}
+
+template <int BITS, bool BF16>
+int launch_tc2(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmTc2Params& p, int grid, size_t smem,
+               cudaStream_t stream) {
+  auto kern = gemm_a16_tc2_kernel<BITS, BF16>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
+  kern<<<grid, kT2Threads, smem, stream>>>(tmx, tmw, p);  // cluster shape comes from __cluster_dims__
+  ASRQ_CUDA_TRY(cudaGetLastError());
+  return ASRQ_OK;
+}
+
+}  // namespace
+
+// The pair kernel needs an even number of feature tiles and enough work for the CTA pairs.
+bool gemm_a16_tc2_supports(int64_t M, int64_t N, int64_t K, int group_size) {
+  return M >= 64 && N % 256 == 0 && K % 64 == 0 && group_size > 0 && group_size % 64 == 0 && K % group_size == 0;
+}
+
+int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+  if (!gemm_a16_tc2_supports(M, N, K, group_size))
+    return fail(ASRQ_ERR_SHAPE, "w%da16 gemm (pair): unsupported shape N=%lld K=%lld g=%d", bits, (long long)N,
+                (long long)K, group_size);
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 24)) return fail(ASRQ_ERR_LIMIT, "w%da16 gemm: size", bits);
+  if (workspace_bytes < kStatusBytes) return fail(ASRQ_ERR_WORKSPACE, "w%da16 gemm: workspace too small", bits);
+  if (!aligned16(x) || !aligned16(w)) return fail(ASRQ_ERR_ALIGN, "w%da16 gemm: x and w must be 16-byte aligned", bits);
+
+  GemmTc2Params p;
+  p.scales = static_cast<const __half*>(scales);
+  p.zeros = static_cast<const __half*>(zeros);
+  p.bias = static_cast<const __half*>(bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.status = static_cast<unsigned*>(workspace);
+  p.M = int(M);
+  p.N = int(N);
+  p.K = int(K);
+  p.group_size = group_size;
+  p.groups_per_row = int(K / group_size);
+  p.n_fpairs = int(N / 256);
+  const int max_clusters = sm_count / 2;
+  p.bt = pick_bt(M, p.n_fpairs, max_clusters);
+  p.n_ttiles = int((M + p.bt - 1) / p.bt);
+  const size_t stage_bytes = size_t(p.bt / 2) * 128 + kT2WSlotBytes;
+  const size_t budget = 227 * 1024 - 1024 - 512 - kT2Slots * kT2ATileBytes;
+  p.nstages = int(std::min<size_t>(kT2MaxStages, budget / stage_bytes));
+  const size_t smem = 1024 + kT2Slots * kT2ATileBytes + p.nstages * stage_bytes;
+
+  const bool bf16 = dtype == ASRQ_BF16;
+  CUtensorMap tmx, tmw;
+  int rc = make_tmap_2d(&tmx, x, 2, bf16, uint64_t(K), uint64_t(M), 64, uint32_t(p.bt / 2), true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmw, w, 1, false, uint64_t(K) * bits / 8, uint64_t(N), uint32_t(8 * bits), 128, false);
+  if (rc) return rc;
+  const int nclusters = int(std::min<int64_t>(int64_t(p.n_fpairs) * p.n_ttiles, max_clusters));
+  const int grid = 2 * nclusters;
+  if (bits == 4)
+    return bf16 ? launch_tc2<4, true>(tmx, tmw, p, grid, smem, stream) : launch_tc2<4, false>(tmx, tmw, p, grid, smem, stream);
+  return bf16 ? launch_tc2<2, true>(tmx, tmw, p, grid, smem, stream) : launch_tc2<2, false>(tmx, tmw, p, grid, smem, stream);
+}
+
+}  // namespace asrq

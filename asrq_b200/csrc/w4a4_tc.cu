@@ -29,6 +29,8 @@
 
 namespace asrq {
 
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 __global__ void __launch_bounds__(256)
 expand_int4_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n_vec) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
@@ -392,7 +394,7 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   else
     kern = fmt == 2 ? (acc_dump ? w4a4_tc_kernel<true, true, 4, 2> : w4a4_tc_kernel<false, true, 4, 2>)
                     : (acc_dump ? w4a4_tc_kernel<true, false, 4, 2> : w4a4_tc_kernel<false, false, 4, 2>);
-  ASRQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
   kern<<<grid, w4a4_threads(tile.cg), smem, stream>>>(tmw, tma, p);
   ASRQ_CUDA_TRY(cudaGetLastError());
   return ASRQ_OK;

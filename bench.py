@@ -162,23 +162,25 @@ class W4A4Config2(Workload):
     def gemm_bytes(self):
         return self.M * self.K + self.N * self.K + self.N * (self.K // self.G) * 2 + self.M * 4 + self.M * self.N * 2
 
-    def step(self, i, ev=None):
-        st = torch.cuda.current_stream().cuda_stream
-        x = self.xs[i % len(self.xs)]
-        L = self.layer
-        if ev:
-            ev[0].record()
-        self.lib.call(L._entry("hadamard_quant"), x.data_ptr(), self.a8.data_ptr(), self.sa.data_ptr(), self.M, self.K,
-                      1, self.lib.F16, st)
-        if ev:
-            ev[1].record()
-        self.lib.call(L._entry("w4a4_gemm"), self.a8.data_ptr(), self.sa.data_ptr(), self.w8.data_ptr(),
-                      L.scales.data_ptr(), L.bias.data_ptr(), self.y.data_ptr(), None, self.M, self.N, self.K, self.G,
-                      self.lib.F16, self.ws.data_ptr(), self.ws.numel(), st)
-        if ev:
-            ev[2].record()
+    nsets = property(lambda self: len(self.xs))
 
-    kernels = [("hadamard_quant", 0, 1), ("w4a4_gemm", 1, 2)]
+    def run_kernel(self, name, i):
+        st = torch.cuda.current_stream().cuda_stream
+        L = self.layer
+        if name == "hadamard_quant":
+            x = self.xs[i % len(self.xs)]
+            self.lib.call(L._entry("hadamard_quant"), x.data_ptr(), self.a8.data_ptr(), self.sa.data_ptr(), self.M,
+                          self.K, 1, self.lib.F16, st)
+        else:
+            self.lib.call(L._entry("w4a4_gemm"), self.a8.data_ptr(), self.sa.data_ptr(), self.w8.data_ptr(),
+                          L.scales.data_ptr(), L.bias.data_ptr(), self.y.data_ptr(), None, self.M, self.N, self.K,
+                          self.G, self.lib.F16, self.ws.data_ptr(), self.ws.numel(), st)
+
+    def step(self, i):
+        self.run_kernel("hadamard_quant", i)
+        self.run_kernel("w4a4_gemm", i)
+
+    kernels = ["hadamard_quant", "w4a4_gemm"]
 
     def e2e_step(self, i):
         xh = self.x_host[i % len(self.x_host)]
@@ -258,18 +260,19 @@ class W4A16Config1(Workload):
         return (2 * self.M * self.K + self.N * self.K // 2 + 2 * self.N * (self.K // self.G) * 2 + 2 * self.N
                 + 2 * self.M * self.N)
 
-    def step(self, i, ev=None):
+    nsets = property(lambda self: len(self.sets))
+
+    def run_kernel(self, name, i):
         st = torch.cuda.current_stream().cuda_stream
         s = self.sets[i % len(self.sets)]
-        if ev:
-            ev[0].record()
         self.lib.call("asrq_w4a16_gemm", s["x"].data_ptr(), s["w"].data_ptr(), s["s"].data_ptr(), s["z"].data_ptr(),
                       s["b"].data_ptr(), s["y"].data_ptr(), self.M, self.N, self.K, self.G, self.lib.F16,
                       self.ws.data_ptr(), self.ws.numel(), st)
-        if ev:
-            ev[1].record()
 
-    kernels = [("gemm_a16_tc", 0, 1)]
+    def step(self, i):
+        self.run_kernel("gemm_a16_tc", i)
+
+    kernels = ["gemm_a16_tc"]
 
     def e2e_step(self, i):
         xh = self.x_host[0]
@@ -331,7 +334,6 @@ class DecodeSweepConfig3(Workload):
         self.copies = 2
         self.items2 = [dict(it, w=it["w"].clone(), s=it["s"].clone(), z=it["z"].clone()) for it in self.items]
         self.launches_per_step = len(self.items)
-        self.graphs = None
         self.ws = torch.zeros(_lib.workspace_bytes(_lib.WS_LINEARQ, 16, 6144, 6144), dtype=torch.uint8, device=device)
         self.l2_note = (f"{len(self.items)} launches per step replayed as one CUDA graph, each on its own weight copy "
                         f"({2 * total >> 20} MiB over two alternating sets > 126 MiB L2)")
@@ -346,33 +348,33 @@ class DecodeSweepConfig3(Workload):
                           it["z"].data_ptr(), None, it["y"].data_ptr(), it["m"], it["n"], it["k"], self.G,
                           self.lib.F16, self.ws.data_ptr(), self.ws.numel(), st)
 
-    def _graphs(self):
-        """The 30 launches of one step captured once per weight set: a decode step is launch-bound
-        when issued call by call from Python, so it is replayed as a CUDA graph."""
-        if self.graphs is None:
-            self._launch_all(self.items)
-            self._launch_all(self.items2)
-            torch.cuda.synchronize()
-            self.graphs = []
-            for items in (self.items, self.items2):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    self._launch_all(items)
-                self.graphs.append(g)
-        return self.graphs
+    nsets = 2
 
-    def step(self, i, ev=None):
-        g = self._graphs()[i % 2]
-        if ev:
-            ev[0].record()
-        g.replay()
-        if ev:
-            ev[1].record()
+    def run_kernel(self, name, i):
+        self._launch_all(self.items if i % 2 == 0 else self.items2)
 
-    kernels = [("gemv_a16 (30 launches)", 0, 1)]
+    def step(self, i):
+        self.run_kernel("gemv_a16 (30 launches)", i)
+
+    kernels = ["gemv_a16 (30 launches)"]
 
     def e2e_step(self, i):
-        return None
+        """The sweep through the C ABI with host activations: every launch's x comes from pinned host
+        memory and its y goes back to pinned host memory."""
+        st = torch.cuda.current_stream().cuda_stream
+        if not hasattr(self, "_host"):
+            self._host = [(it["x"].cpu().pin_memory(), torch.empty(it["m"], it["n"], dtype=torch.float16).pin_memory())
+                          for it in self.items]
+        h2d = d2h = 0
+        for it, (xh, yh) in zip(self.items if i % 2 == 0 else self.items2, self._host):
+            xd = xh.to(self.dev, non_blocking=True)
+            self.lib.call(f"asrq_w{it['bits']}a16_gemv", xd.data_ptr(), it["w"].data_ptr(), it["s"].data_ptr(),
+                          it["z"].data_ptr(), None, it["y"].data_ptr(), it["m"], it["n"], it["k"], self.G,
+                          self.lib.F16, self.ws.data_ptr(), self.ws.numel(), st)
+            yh.copy_(it["y"], non_blocking=True)
+            h2d += xh.numel() * 2
+            d2h += yh.numel() * 2
+        return h2d, d2h
 
     def roofline(self, kernel_ms, peaks, int8_tops):
         ach = self.total_bytes / (kernel_ms["gemv_a16 (30 launches)"] * 1e-3) / 1e9
@@ -496,13 +498,31 @@ def main():
     _lib.load()
     peaks = measured_peaks()
 
+    def capture(fn, n):
+        """One CUDA graph per input set: a step issued call by call from Python is bound by the host (the
+        ctypes call and the launch cost as much as these kernels run), so steps are replayed as graphs."""
+        graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(n):
+                fn(i)
+            torch.cuda.synchronize()
+            for i in range(n):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    fn(i)
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        return graphs
+
     def measure(name, steps, warmup, with_e2e):
         wl = WORKLOADS[name](device, args.seed + 1000 * rank)
+        graphs = capture(wl.step, wl.nsets)
         for i in range(warmup):
-            wl.step(i)
+            graphs[i % wl.nsets].replay()
         torch.cuda.synchronize()
-        nk = max(e for _, _, e in wl.kernels) + 1
-        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nk)] for _ in range(steps)]
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
@@ -511,15 +531,28 @@ def main():
         t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t_start.record()
         for i in range(steps):
-            wl.step(warmup + i, evs[i])
+            graphs[(warmup + i) % wl.nsets].replay()
         t_end.record()
         torch.cuda.synchronize()
         dp.barrier()
         clocks = sampler.stop() if rank == 0 else None
         total_ms = dp.max_over_ranks(t_start.elapsed_time(t_end))
+        # each kernel alone, the same way (outside the timed region of the step)
         kernel_ms = {}
-        for kname, a, b in wl.kernels:
-            kernel_ms[kname] = sum(ev[a].elapsed_time(ev[b]) for ev in evs) / steps
+        if len(wl.kernels) == 1:
+            kernel_ms[wl.kernels[0]] = t_start.elapsed_time(t_end) / steps
+        else:
+            for kname in wl.kernels:
+                kg = capture(lambda i, kname=kname: wl.run_kernel(kname, i), wl.nsets)
+                for i in range(3):
+                    kg[i % wl.nsets].replay()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for i in range(steps):
+                    kg[i % wl.nsets].replay()
+                b.record()
+                torch.cuda.synchronize()
+                kernel_ms[kname] = a.elapsed_time(b) / steps
         e2e = None
         if with_e2e and wl.e2e_step(0) is not None:
             for i in range(3):
@@ -537,7 +570,8 @@ def main():
             scale = 1e12 if wl.unit in ("TOP/s", "TFLOP/s") else 1e9
             e2e = {"value": wl.units_per_step() * world / (e2e_ms * 1e-3) / scale, "unit": wl.unit,
                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                   "api": f"asrq_b200.{type(wl.layer).__name__}.forward on a pinned host tensor, result copied to pinned host memory"}
+                   "api": (f"asrq_b200.{type(wl.layer).__name__}.forward on a pinned host tensor, result copied to pinned host memory"
+                           if hasattr(wl, "layer") else "the C-ABI decode calls with pinned host activations in and pinned host outputs back")}
         _lib.call("asrq_check_status", wl.ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
         return wl, total_ms / steps, kernel_ms, clocks, e2e
 
@@ -551,6 +585,7 @@ def main():
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
         "config": {"workload": f"{wl.name}: " + (wl.__doc__ or "").strip(), "per_gpu": "every rank runs the full step "
                    "on its own replica and batch; no data-path collective", "l2": wl.l2_note,
+                   "launch": "each step is one CUDA-graph replay, captured once per input set (a step issued call by call from Python is host-bound)",
                    "M": getattr(wl, "M", None), "K": getattr(wl, "K", None), "N": getattr(wl, "N", None)},
         "kernel_ms": kernel_ms, "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks,
     }

@@ -168,3 +168,16 @@ def test_module_dispatch_and_leading_dims():
     assert empty.shape == (0, 3, 16, 1280)
     with pytest.raises(TypeError):
         lq(x.float())
+
+
+@pytest.mark.parametrize("m,k,n,bits", [(64, 256, 256, 4), (300, 1280, 1024, 4), (1500, 1280, 5120, 4), (200, 1024, 512, 2)])
+def test_gemm_cta_pair_variant(m, k, n, bits, monkeypatch):
+    """The opt-in tcgen05 cta_group::2 kernel (two CTAs share one 256-row MMA) against the fp32 CPU result."""
+    monkeypatch.setenv("ASRQ_B200_TC_PAIR", "1")
+    gen = torch.Generator().manual_seed(m + n)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, 128, False)
+    case = dict(x=torch.randn(m, k, generator=gen).half(), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half(), bits=bits, group_size=128)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemm", case)
+    assert_close_rows(y, _ref32(case, torch.float16), what=f"pair gemm w{bits} m{m}")
