@@ -468,7 +468,16 @@ def run_reference(args, rank):
                              "sample": sample},
             "e2e": {"value": v, "unit": cls.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    emit(line)
+
+
+_RESULT_OUT = sys.stdout
+
+
+def emit(line):
+    """Writes the result line to the process's original standard output."""
+    _RESULT_OUT.write(json.dumps(line) + "\n")
+    _RESULT_OUT.flush()
 
 
 def main():
@@ -614,9 +623,14 @@ def main():
         line["also"] = also
     dp.barrier()
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     dp.finalize()
 
 
 if __name__ == "__main__":
+    # Standard output carries the one result line and nothing else: libraries that write to file
+    # descriptor 1 (NCCL's version banner) are sent to standard error instead.
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     main()
