@@ -16,6 +16,7 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
              void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
              size_t workspace_bytes, int sm_count, cudaStream_t stream, int max_split);
 size_t gemv_workspace_bytes(int64_t N);
+size_t gemm_tc_workspace_bytes(int64_t M, int64_t N);
 int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
                 size_t workspace_bytes, int sm_count, cudaStream_t stream);
@@ -226,7 +227,7 @@ size_t asrq_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
     case ASRQ_WS_LINEARQ:
       return gemv_workspace_bytes(N);
     case ASRQ_WS_A16_GEMM:
-      return kStatusBytes;
+      return gemm_tc_workspace_bytes(M, N);
     case ASRQ_WS_W4A4_GEMM:
       return w4a4_tc_workspace_bytes(M, N, K);
     default:

@@ -38,8 +38,33 @@ struct GemmTcParams {
   uint16_t* y;
   unsigned* status;
   long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
+  float* partials;    // split-K: fp32 partial tiles [tile][split][bt tokens][128 features]
+  unsigned* counters; // split-K: one arrival counter per (tile, lane quadrant), zero between launches
   int M, N, K, group_size, groups_per_row, bt, nstages, n_ftiles, n_ttiles;
+  int ksplit;         // parts the K blocks of a tile are divided into (1: no split)
 };
+
+// One unit of work of a block: the K blocks [kb0, kb1) of output tile (ft, tt).  Items are numbered
+// with the split index fastest, so the parts of a tile run on neighbouring blocks at the same time.
+struct TcItem {
+  int ft, tt, ks, kb0, kb1;
+};
+__device__ __forceinline__ TcItem tc_item(const GemmTcParams& p, int w, int nkb) {
+  TcItem it;
+  if (p.ksplit == 1) {
+    it.ks = 0;
+    it.kb0 = 0;
+    it.kb1 = nkb;
+  } else {
+    it.ks = w % p.ksplit;
+    w /= p.ksplit;
+    it.kb0 = it.ks * nkb / p.ksplit;
+    it.kb1 = (it.ks + 1) * nkb / p.ksplit;
+  }
+  it.ft = w % p.n_ftiles;
+  it.tt = w / p.n_ftiles;
+  return it;
+}
 
 constexpr int kTcDequantGroups = 3;
 constexpr int kTcWarps = 20;
@@ -52,6 +77,7 @@ constexpr int kTcMmaWarp = 1, kTcProducerWarp = 9;
 // position of a warp among the twelve dequant warps (-1: not a dequant warp)
 __constant__ int8_t kTcDequantPos[kTcWarps] = {0, -1, -1, -1, -1, -1, 1, 2, 3, -1, 4, 5, 6, -1, 7, 8, 9, -1, 10, 11};
 constexpr int kTcMaxStages = 8;
+constexpr int64_t kTcMaxSplit = 8;  // the last block to arrive reads every part: one trip to L2 each
 constexpr uint32_t kATileBytes = 128 * 128;  // one dequantised A slot: 128 rows x 64 16-bit elements
 constexpr uint32_t kWSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
 
@@ -109,8 +135,8 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
   tc::fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
 
-  const int ntiles = p.n_ftiles * p.n_ttiles;
   const int nkb = p.K / 64;
+  const int nitems = p.n_ftiles * p.n_ttiles * p.ksplit;
   const bool tr = p.trace != nullptr && blockIdx.x == 0;
   auto mark = [&](int role, uint32_t i, int slot) {
     if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
@@ -126,10 +152,10 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       uint32_t it = 0, ph = 0;
       int s = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
-        const int row_x = tt * p.bt, row_w = ft * 128;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+        const TcItem item = tc_item(p, w, nkb);
+        const int row_x = item.tt * p.bt, row_w = item.ft * 128;
+        for (int kb = item.kb0; kb < item.kb1; ++kb, ++it) {
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
           mark(0, it, 0);
           const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
@@ -147,42 +173,46 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
     // pipe starves unless the next issue follows within one MMA time (~110 cycles, ~15 dependent
     // instructions of this lone thread).  All bookkeeping for the NEXT K block -- ring counters,
     // barrier waits -- is therefore placed between the four issues of the current one.
-    if (lane == 0) {
+    {
+      const bool el = tc::elect_one();
       const uint32_t idesc = tc::instr_desc(1u, BF16 ? 1u : 0u, 128u, uint32_t(p.bt));
       uint32_t it = 0, tcount = 0, ph = 0, dph = 0;
       int s = 0, a = 0;
-      bool ok = ntiles > int(blockIdx.x);
+      bool ok = nitems > int(blockIdx.x);
       if (ok) {
         ok = tc::mbar_wait_spin(acce_bar(0), 1u, p.status, 2) && tc::mbar_wait_spin(deq_bar(0), 0u, p.status, 4);
         tc::fence_after_sync();
       }
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+      for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x, ++tcount) {
+        const TcItem item = tc_item(p, w, nkb);
         const uint32_t buf = tcount & 1u;
         const uint32_t d_tmem = tmem_base + buf * 256u;
-        const bool more_tiles = tile + int(gridDim.x) < ntiles;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const bool more_tiles = w + int(gridDim.x) < nitems;
+        for (int kb = item.kb0; kb < item.kb1; ++kb, ++it) {
           mark(1, it, 0);
           // a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address field
           const uint64_t da = tc::smem_desc_sw128(base + a * kATileBytes);
           const uint64_t db = tc::smem_desc_sw128(base + a_ring_bytes + s * stage_bytes);
-          tc::mma_f16(d_tmem, da, db, idesc, uint32_t(kb != 0));
+          if (el) tc::mma_f16(d_tmem, da, db, idesc, uint32_t(kb != item.kb0));
           // next K block's ring positions
           int s1 = s + 1, a1 = a + 1;
           uint32_t ph1 = ph, dph1 = dph;
           if (s1 == nst) { s1 = 0; ph1 ^= 1u; }
           if (a1 == kTcDequantGroups) { a1 = 0; dph1 ^= 1u; }
-          const bool last_kb = kb + 1 == nkb;
+          const bool last_kb = kb + 1 == item.kb1;
           const bool have_next = !last_kb || more_tiles;
-          tc::mma_f16(d_tmem, da + 2, db + 2, idesc, 1u);
-          tc::mma_f16(d_tmem, da + 4, db + 4, idesc, 1u);
+          if (el) tc::mma_f16(d_tmem, da + 2, db + 2, idesc, 1u);
+          if (el) tc::mma_f16(d_tmem, da + 4, db + 4, idesc, 1u);
           // deq[a1] completing implies full[s1]: the dequant group of the next block waited for that
           // stage's TMA before it wrote the A slot and arrived (release), and this wait acquires it
           if (have_next) ok = tc::mbar_wait_spin(deq_bar(a1), dph1, p.status, 4);
-          tc::mma_f16(d_tmem, da + 6, db + 6, idesc, 1u);
+          if (el) tc::mma_f16(d_tmem, da + 6, db + 6, idesc, 1u);
           // one commit frees both the TMA stage (producer) and the A slot (dequant group waits on
           // the empty barrier of the stage its previous block used)
-          tc::mma_commit(empty_bar(s));
-          if (last_kb) tc::mma_commit(accf_bar(buf));
+          if (el) {
+            tc::mma_commit(empty_bar(s));
+            if (last_kb) tc::mma_commit(accf_bar(buf));
+          }
           if (have_next && last_kb && ok) {  // the next tile's accumulator buffer must have been drained
             const uint32_t nt = tcount + 1;
             ok = tc::mbar_wait_spin(acce_bar(nt & 1u), ((nt >> 1) & 1u) ^ 1u, p.status, 2);
@@ -198,33 +228,41 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
     const int t = (dpos & 3) * 32 + lane;  // weight row inside the tile
     const int dgroup = dpos >> 2;          // this warp group takes K blocks dgroup, dgroup+3, ...
     constexpr int NDG = kTcDequantGroups;
-    // position of the K block being processed and of the next one (for the scale/zero prefetch)
-    int tile = blockIdx.x, kb = dgroup;
-    while (kb >= nkb && tile < ntiles) { kb -= nkb; tile += gridDim.x; }
+    // position (item, K block) of the block being processed; `advance` moves a position NDG blocks
+    // along this block's sequence of items (an item has at least one K block)
+    int w = blockIdx.x;
+    TcItem item = tc_item(p, w < nitems ? w : 0, nkb);
+    int kb = item.kb0;
+    auto advance = [&](int& aw, TcItem& ai, int& ak, int by) {
+      ak += by;
+      while (aw < nitems && ak >= ai.kb1) {
+        const int over = ak - ai.kb1;
+        aw += gridDim.x;
+        if (aw < nitems) {
+          ai = tc_item(p, aw, nkb);
+          ak = ai.kb0 + over;
+        }
+      }
+    };
+    advance(w, item, kb, dgroup);
     int s = dgroup % nst;
     uint32_t ph = (dgroup / nst) & 1u, dph = 0, it = dgroup;
     const int kbpg = p.group_size / 64;  // K blocks per weight group
-    const int ft_step = int(gridDim.x) % p.n_ftiles;
-    int ft = tile % p.n_ftiles;          // feature tile of `tile`, advanced without division
     auto load_sz = [&](int f, int k) -> uint32_t {
       const int gi = kbpg == 1 ? k : (kbpg == 2 ? (k >> 1) : k / kbpg);
       const size_t idx = (size_t(f) * 128 + t) * p.groups_per_row + gi;
       return uint32_t(__half_as_ushort(__ldg(p.scales + idx))) | (uint32_t(__half_as_ushort(__ldg(p.zeros + idx))) << 16);
     };
-    uint32_t sz_next = tile < ntiles ? load_sz(ft, kb) : 0u;
+    uint32_t sz_next = w < nitems ? load_sz(item.ft, kb) : 0u;
     bool ok = true, first = true;
     int s_prev = 0;
     uint32_t ph_prev = 0;
-    while (tile < ntiles && ok) {
+    while (w < nitems && ok) {
       const uint32_t sz = sz_next;
-      int ntile = tile, nk = kb + NDG;
-      while (nk >= nkb && ntile < ntiles) {
-        nk -= nkb;
-        ntile += gridDim.x;
-        ft += ft_step;
-        if (ft >= p.n_ftiles) ft -= p.n_ftiles;
-      }
-      if (ntile < ntiles) sz_next = load_sz(ft, nk);  // consumed three K blocks from now
+      int nw = w, nk = kb;
+      TcItem nitem = item;
+      advance(nw, nitem, nk, NDG);
+      if (nw < nitems) sz_next = load_sz(nitem.ft, nk);  // consumed three K blocks from now
       const __half sh = __ushort_as_half(uint16_t(sz & 0xffffu)), zh = __ushort_as_half(uint16_t(sz >> 16));
       uint32_t s2, z2;
       if (BF16) {
@@ -270,7 +308,8 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(deq_bar(dgroup));
       if (t == 0) mark(2, it, 1);
-      tile = ntile;
+      w = nw;
+      item = nitem;
       kb = nk;
       it += NDG;
       dph ^= 1u;
@@ -282,8 +321,9 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
     const int qd = warp & 3;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-      const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+    for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x, ++tcount) {
+      const TcItem item = tc_item(p, w, nkb);
+      const int ft = item.ft, tt = item.tt;
       const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
       const int f = ft * 128 + qd * 32 + lane;
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
@@ -295,6 +335,56 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       // (64 contiguous bytes) of that token's row; the row pointer advances by N per column
       uint16_t* yp = p.y + size_t(tt) * p.bt * p.N + f;
       const int rows_left = p.M - tt * p.bt;  // tokens of this tile that exist
+      if (p.ksplit > 1) {
+        // Split K: this block's part of the tile goes to the workspace as fp32 ([token][feature], a
+        // warp writes 128 contiguous bytes per token); the warp that arrives last for its 32
+        // features adds the parts in split order (so the result does not depend on timing), adds
+        // the bias, converts and stores.  Each lane quadrant synchronises by itself through its own
+        // counter, which the last warp leaves at zero for the next launch.
+        const int tile = tt * p.n_ftiles + ft;
+        const size_t part_elems = size_t(p.bt) * 128;
+        float* part0 = p.partials + size_t(tile) * p.ksplit * part_elems + qd * 32 + lane;
+        float* mine = part0 + size_t(item.ks) * part_elems;
+        for (int ch = 0; ch < p.bt / 32; ++ch) {
+          uint32_t r[32];
+          tc::tmem_ld_32x32(taddr + ch * 32, r);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) __stcg(mine + size_t(ch * 32 + j) * 128, __uint_as_float(r[j]));
+        }
+        tc::fence_before_sync();
+        tc::mbar_arrive(acce_bar(buf));
+        __threadfence();
+        __syncwarp();
+        unsigned prev = 0;
+        if (lane == 0) prev = atomicAdd(p.counters + tile * 4 + qd, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == unsigned(p.ksplit - 1)) {
+          __threadfence();
+          // 32 tokens at a time, one load per token in flight per lane: a part costs one trip to L2
+          for (int ch = 0; ch * 32 < rows_left && ch < p.bt / 32; ++ch) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            const float* src = part0 + size_t(ch) * 32 * 128;
+            for (int ks = 0; ks < p.ksplit; ++ks, src += part_elems) {
+              float a[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) a[j] = __ldcg(src + j * 128);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += a[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (ch * 32 + j < rows_left) *yp = float_to_out16(v[j] + bias, BF16);
+              yp += p.N;
+            }
+          }
+          if (lane == 0) p.counters[tile * 4 + qd] = 0u;
+        }
+        if (warp == 4 && lane == 0) mark(3, tcount, 1);
+        continue;
+      }
       for (int ch = 0; ch < p.bt / 32; ++ch) {
         uint32_t r[32];
         tc::tmem_ld_32x32(taddr + ch * 32, r);
@@ -349,6 +439,22 @@ int gemm_tc_pick_bt(int64_t M, int64_t N, int sm_count) {
     }
   }
   return best;
+}
+
+// Split K (mid-size M): with few output tiles most SMs would idle while each busy one walks the
+// whole K range, so the K blocks of a tile are divided among `split` blocks.  Bounded by the SM
+// count, by two K blocks per part, and by the partial-sum area the workspace contract provides
+// (split x padded M <= 512, the skinny kernel's 2048 bytes per output feature).
+int gemm_tc_pick_split(int64_t M, int64_t N, int64_t K, int bt, int sm_count) {
+  if (const char* e = getenv("ASRQ_B200_TC_SPLIT")) {  // tuning knob: 1 disables
+    if (atoi(e) == 1) return 1;
+  }
+  const int64_t n_tt = (M + bt - 1) / bt, tiles = (N / 128) * n_tt, nkb = K / 64;
+  int64_t split = std::min<int64_t>({int64_t(sm_count) / tiles, nkb / 2, 512 / (n_tt * bt), kTcMaxSplit});
+  return int(std::max<int64_t>(split, 1));
+}
+size_t gemm_tc_workspace_bytes(int64_t M, int64_t N) {
+  return M <= 256 ? kPartialOffset + size_t(2048) * size_t(N) : kStatusBytes;
 }
 
 template <int BITS, bool BF16>
@@ -412,7 +518,13 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
   if (rc) return rc;
   rc = make_tmap_2d(&tmw, w, 1, false, uint64_t(K) * bits / 8, uint64_t(N), uint32_t(8 * bits), 128, false);
   if (rc) return rc;
-  const int grid = int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles, sm_count));
+  p.ksplit = gemm_tc_pick_split(M, N, K, p.bt, sm_count);
+  if (p.ksplit > 1 && (workspace_bytes < kPartialOffset + size_t(4) * N * p.n_ttiles * p.bt * p.ksplit ||
+                       p.n_ftiles * p.n_ttiles * 4 > int(kCounterBytes / sizeof(unsigned))))
+    p.ksplit = 1;
+  p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + kPartialOffset);
+  p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kStatusBytes);
+  const int grid = int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles * p.ksplit, sm_count));
   if (bits == 4)
     return bf16 ? launch_tc<4, true>(tmx, tmw, p, grid, smem, stream) : launch_tc<4, false>(tmx, tmw, p, grid, smem, stream);
   return bf16 ? launch_tc<2, true>(tmx, tmw, p, grid, smem, stream) : launch_tc<2, false>(tmx, tmw, p, grid, smem, stream);

@@ -145,6 +145,13 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t dfmt, uint32_t abfmt, ui
 }
 
 // ---- MMA (single thread) -----------------------------------------------------------------
+// One lane of a converged warp.  A role loop that the whole warp runs, with only the tcgen05
+// instructions under this predicate, keeps its counters, addresses and descriptors warp-uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(

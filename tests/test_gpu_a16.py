@@ -122,6 +122,50 @@ def test_gemm_tc_shapes(bits, g, m, k, n, bias):
     assert_close_rows(y, _ref32(case), what=f"gemm w{bits} g{g} m{m} {k}x{n}")
 
 
+@pytest.mark.parametrize("bits,g,m,k,n,bias,dtype", [
+    (4, 128, 32, 2048, 6144, False, torch.float16),   # decode batch 32: 48 tiles, K in 3 parts
+    (4, 128, 64, 5120, 1280, True, torch.float16),    # 20 tiles, K in 7 parts
+    (2, 64, 40, 1280, 1280, True, torch.float16),     # ragged M, two token tiles
+    (4, 64, 100, 6144, 2048, False, torch.bfloat16),
+    (4, 128, 256, 1280, 1280, True, torch.float16),   # widest M that still splits
+])
+def test_gemm_tc_split_k(bits, g, m, k, n, bias, dtype):
+    """Mid-size M: the K range of a tile is divided among blocks and the fp32 parts are added in a
+    fixed order by the last block to arrive.  Same workspace for two calls: the tile counters must
+    come back to zero, and the result must not depend on timing."""
+    gen = torch.Generator().manual_seed(bits * 11 + m)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen).to(dtype), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half() if bias else None,
+                bits=bits, group_size=g)
+    from asrq_b200 import _lib
+    x, wq = case["x"].to(DEV), case["weight"].to(DEV)
+    sc, ze = case["scales"].to(DEV), case["zeros"].to(DEV)
+    b = None if case["bias"] is None else case["bias"].to(DEV)
+    ws = torch.zeros(_lib.workspace_bytes(_lib.WS_A16_GEMM, m, n, k), dtype=torch.uint8, device=DEV)
+    assert ws.numel() > 16640
+    ys = []
+    for _ in range(2):
+        y = torch.empty(m, n, dtype=dtype, device=DEV)
+        _lib.call(f"asrq_w{bits}a16_gemm", x.data_ptr(), wq.data_ptr(), sc.data_ptr(), ze.data_ptr(),
+                  None if b is None else b.data_ptr(), y.data_ptr(), m, n, k, g,
+                  _lib.F16 if dtype == torch.float16 else _lib.BF16, ws.data_ptr(), ws.numel(),
+                  torch.cuda.current_stream().cuda_stream)
+        _lib.call("asrq_check_status", ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert int(ws[:16640].view(torch.int32).abs().sum()) == 0, "status block or tile counters not clean"
+        ys.append(y)
+    assert torch.equal(ys[0], ys[1])
+    ref = _ref32(case, dtype)
+    if dtype == torch.float16:
+        assert_close_rows(ys[0], ref, what=f"split-K gemm w{bits} m{m} {k}x{n}")
+    else:
+        wd = O.dequantize_weight(case["weight"], case["scales"], case["zeros"], bits, g, k, torch.float32)
+        xf = case["x"].float()
+        w_round = 6.0 * 2.0 ** -9 / 3 ** 0.5 * torch.sqrt((xf * xf) @ (wd * wd).t())
+        assert_close_rows(ys[0], ref, rel=2e-3, extra=bf16_half_ulp(ref) + w_round, what="split-K gemm bf16")
+
+
 @pytest.mark.parametrize("bits", [4, 2])
 def test_gemm_tc_bf16(bits):
     gen = torch.Generator().manual_seed(bits)
