@@ -416,7 +416,11 @@ GemvSplit gemv_pick_split(int bits, int mh, int gps, bool xc, bool trace, int64_
     }
     const long slots = long(per_sm) * sm_count;
     const long waves = (long(N / 16) + slots - 1) / slots;
-    if (!best.kern || waves < best_waves) {  // candidates come in order of decreasing warp count
+    // Fewest waves first.  Among those, 8 to 12 warps per block measured fastest on the decode
+    // shapes (16 warps pay more for the shared-memory reduction and the block-wide barrier, 4 to 6
+    // leave too few loads in flight): the largest count up to 12, else the smallest above.
+    auto rank = [](int q) { return q <= 12 ? 100 - q : 100 + q; };
+    if (!best.kern || waves < best_waves || (waves == best_waves && rank(kq) < rank(best.KQ))) {
       best = {kq, cpw, k};
       best_waves = waves;
     }
