@@ -41,6 +41,7 @@ struct GemvParams {
   const __half* bias;
   uint16_t* y;
   int M, N, K, groups_per_row, KQ, CPW, bf16;  // CPW repeats the kernel's template argument
+  int R;                                       // rounds (LOOP variants): a warp takes R runs of CPW steps, KQ * CPW steps apart
   unsigned long long* trace;  // diagnostic: per-warp clock marks (8 words per warp), NULL normally
 };
 
@@ -127,8 +128,15 @@ __device__ __forceinline__ unsigned long long gemv_globaltimer() {
 // (1, 2 or 4; the group size is 128/GPS k for 4-bit and 256/GPS k for 2-bit).  CPW: steps per warp
 // (1, 2 or 4, CPW * GPS <= 8).  XC: M <= 2, the activation sums are made on the CUDA cores instead of
 // by an MMA against ones (the legacy MMA pipe is this kernel's second bottleneck).
-template <int BITS, int MH, int GPS, int CPW, bool XC, bool TRACE>
-__global__ void __launch_bounds__(kGemvMaxWarps * 32, (CPW == 1 && MH == 1 && BITS == 4) ? 3 : 1) gemv_a16_kernel(const GemvParams p) {
+// LOOP: layers too large for one resident wave.  Blocks are small (a few warps), several share an SM
+// at different points of their lives, and a warp walks K in R rounds, so that loads of one block
+// are in flight while another computes.  (Measured on 32-128 MB layers at M=1: 2.7-3.4 TB/s against
+// 2.0-2.5 for one round per warp.  Requesting the next round's words before this round's arithmetic,
+// in registers or through a cp.async ring in shared memory, measured slower: the variant is bound by
+// per-warp latency with 12-16 warps per SM at 128 registers, not by bytes in flight.)
+template <int BITS, int MH, int GPS, int CPW, bool XC, bool TRACE, bool LOOP = false>
+__global__ void __launch_bounds__(kGemvMaxWarps * 32, (CPW == 1 && MH == 1 && BITS == 4 && !LOOP) ? 3 : 1)
+gemv_a16_kernel(const GemvParams p) {
   constexpr int CPWORD = 32 / BITS;   // codes per 32-bit word (8 / 16)
   constexpr int STEPK = 16 * CPWORD;  // k per step (128 / 256)
   constexpr int NT = 8 / BITS;        // field positions inside a byte = accumulator types (2 / 4)
@@ -155,43 +163,47 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (CPW == 1 && MH == 1 && BI
     }
   }
   constexpr int NG = CPW * GPS;       // groups per warp
-  const int step0 = warp * CPW;
   const size_t row_bytes = size_t(p.K) * BITS / 8;
-  // word (j, t) of step i sits at byte i*64 + j*(64/GPS) + c*(16/GPS) + 4*t of the warp's row span
-  const uint8_t* w0 = p.w + size_t(r0) * row_bytes + size_t(step0) * 64 + c * (16 / GPS);
-  const uint8_t* w1 = w0 + 8 * row_bytes;
-
-  // Let the next kernel on the stream start, and start streaming weights before this kernel's
-  // own predecessor has finished: weights, scales and zeros are constants; only the activations
-  // and the output depend on earlier kernels.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  uint32_t qa[CPW][4], qb[CPW][4];
-#pragma unroll
-  for (int i = 0; i < CPW; ++i) {
-#pragma unroll
-    for (int j = 0; j < GPS; ++j) {
-      ldg_stream_words<WPC>(w0 + i * 64 + j * (64 / GPS), &qa[i][j * WPC]);
-      ldg_stream_words<WPC>(w1 + i * 64 + j * (64 / GPS), &qb[i][j * WPC]);
-    }
-  }
-  // scale and zero of this warp's NG = CPW * GPS groups, rows g and g+8
-  uint32_t ts0[4], tz0[4], ts1[4], tz1[4];
-  {
-    const size_t o0 = size_t(r0) * p.groups_per_row + size_t(step0) * GPS;
-    const size_t o1 = o0 + size_t(8) * p.groups_per_row;
-    load_group_table<NG>(p.scales + o0, ts0);
-    load_group_table<NG>(p.zeros + o0, tz0);
-    load_group_table<NG>(p.scales + o1, ts1);
-    load_group_table<NG>(p.zeros + o1, tz1);
-  }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (TRACE && lane == 0) tr[2] = gemv_clock();
-
   float yv[MH][4];
 #pragma unroll
   for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
     for (int i = 0; i < 4; ++i) yv[mh][i] = 0.f;
+  // Let the next kernel on the stream start, and start streaming weights before this kernel's
+  // own predecessor has finished: weights, scales and zeros are constants; only the activations
+  // and the output depend on earlier kernels.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int rounds = LOOP ? p.R : 1;
+  // word (j, t) of step i sits at byte i*64 + j*(64/GPS) + c*(16/GPS) + 4*t of the warp's row span
+  auto row_ptr = [&](int step0) { return p.w + size_t(r0) * row_bytes + size_t(step0) * 64 + c * (16 / GPS); };
+  // scale and zero of the warp's NG = CPW * GPS groups of a round, rows g and g+8
+  auto load_tables = [&](int step0, uint32_t (&s0)[4], uint32_t (&z0)[4], uint32_t (&s1)[4], uint32_t (&z1)[4]) {
+    const size_t o0 = size_t(r0) * p.groups_per_row + size_t(step0) * GPS;
+    const size_t o1 = o0 + size_t(8) * p.groups_per_row;
+    load_group_table<NG>(p.scales + o0, s0);
+    load_group_table<NG>(p.zeros + o0, z0);
+    load_group_table<NG>(p.scales + o1, s1);
+    load_group_table<NG>(p.zeros + o1, z1);
+  };
+  uint32_t qa[CPW][4], qb[CPW][4], ts0[4], tz0[4], ts1[4], tz1[4];
+#pragma unroll 1
+  for (int rd = 0; rd < rounds; ++rd) {
+  const int step0 = (rd * p.KQ + warp) * CPW;
+  {
+    const uint8_t* w0 = row_ptr(step0);
+    const uint8_t* w1 = w0 + 8 * row_bytes;
+#pragma unroll
+    for (int i = 0; i < CPW; ++i) {
+#pragma unroll
+      for (int j = 0; j < GPS; ++j) {
+        ldg_stream_words<WPC>(w0 + i * 64 + j * (64 / GPS), &qa[i][j * WPC]);
+        ldg_stream_words<WPC>(w1 + i * 64 + j * (64 / GPS), &qb[i][j * WPC]);
+      }
+    }
+    load_tables(step0, ts0, tz0, ts1, tz1);
+  }
+  if (rd == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (TRACE && lane == 0) tr[2] = gemv_clock();
 
   // XC: sum of x over each of the warp's groups for tokens 0 and 1, the same in every lane.  The
   // warp's k span is cut into 32 runs, one per lane; a group is 32/NG consecutive lanes.  The loads
@@ -325,6 +337,7 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, (CPW == 1 && MH == 1 && BI
       }
     }
   }
+  }  // rounds
   if (TRACE && lane == 0) tr[5] = gemv_clock_after(__float_as_uint(yv[0][0]));
 
   // ---- add the KQ partial tiles through shared memory (fixed order) and write the strip ---------
@@ -383,6 +396,30 @@ GemvKernel kernel_for(int gps, int cpw, bool xc, bool trace) {
     default: return nullptr;
   }
 }
+// LOOP variants: the most steps per round the group table allows (CPW * GPS <= 8), no trace build
+template <int BITS, int MH>
+GemvKernel loop_kernel_for(int gps, bool xc, int* cpw) {
+  *cpw = gps == 4 ? 2 : 4;
+  if (MH == 1 && xc) {
+    switch (gps) {
+      case 1: return gemv_a16_kernel<BITS, 1, 1, 4, true, false, true>;
+      case 2: return gemv_a16_kernel<BITS, 1, 2, 4, true, false, true>;
+      case 4: return gemv_a16_kernel<BITS, 1, 4, 2, true, false, true>;
+      default: return nullptr;
+    }
+  }
+  switch (gps) {
+    case 1: return gemv_a16_kernel<BITS, MH, 1, 4, false, false, true>;
+    case 2: return gemv_a16_kernel<BITS, MH, 2, 4, false, false, true>;
+    case 4: return gemv_a16_kernel<BITS, MH, 4, 2, false, false, true>;
+    default: return nullptr;
+  }
+}
+GemvKernel loop_kernel_for(int bits, int mh, int gps, bool xc, int* cpw) {
+  if (bits == 4) return mh == 1 ? loop_kernel_for<4, 1>(gps, xc, cpw) : loop_kernel_for<4, 2>(gps, xc, cpw);
+  return mh == 1 ? loop_kernel_for<2, 1>(gps, xc, cpw) : loop_kernel_for<2, 2>(gps, xc, cpw);
+}
+
 GemvKernel kernel_for(int bits, int mh, int gps, int cpw, bool xc, bool trace) {
   if (bits == 4) return mh == 1 ? kernel_for<4, 1>(gps, cpw, xc, trace) : kernel_for<4, 2>(gps, cpw, xc, trace);
   return mh == 1 ? kernel_for<2, 1>(gps, cpw, xc, trace) : kernel_for<2, 2>(gps, cpw, xc, trace);
@@ -395,13 +432,16 @@ GemvKernel kernel_for(int bits, int mh, int gps, int cpw, bool xc, bool trace) {
 struct GemvSplit {
   int KQ, CPW;
   GemvKernel kern;
+  int R = 1;        // rounds per warp (LOOP variants)
 };
 
 GemvSplit gemv_pick_split(int bits, int mh, int gps, bool xc, bool trace, int64_t N, int64_t K, int sm_count) {
   const int stepk = bits == 4 ? 128 : 256;
   const int steps = int(K / stepk);
   static const int cpw_env = getenv("ASRQ_B200_GEMV_CPW") ? atoi(getenv("ASRQ_B200_GEMV_CPW")) : 0;  // tuning knob
-  GemvSplit best = {0, 0, nullptr};
+  GemvSplit best;
+  best.KQ = best.CPW = 0;
+  best.kern = nullptr;
   long best_waves = 0;
   for (int cpw = 1; cpw <= kGemvMaxSteps; cpw *= 2) {
     if (steps % cpw || steps / cpw > kGemvMaxWarps || cpw * gps > 8) continue;
@@ -421,8 +461,28 @@ GemvSplit gemv_pick_split(int bits, int mh, int gps, bool xc, bool trace, int64_
     // leave too few loads in flight): the largest count up to 12, else the smallest above.
     auto rank = [](int q) { return q <= 12 ? 100 - q : 100 + q; };
     if (!best.kern || waves < best_waves || (waves == best_waves && rank(kq) < rank(best.KQ))) {
-      best = {kq, cpw, k};
+      best.KQ = kq;
+      best.CPW = cpw;
+      best.kern = k;
       best_waves = waves;
+    }
+  }
+  // Layers that do not fit one resident wave (or whose K is longer than 16 warps x 4 steps): small
+  // blocks that walk K in rounds, so that the blocks sharing an SM overlap loads and arithmetic.
+  static const int loop_env = getenv("ASRQ_B200_GEMV_LOOP") ? atoi(getenv("ASRQ_B200_GEMV_LOOP")) : -1;  // tuning knob
+  const bool large = N * K * bits / 8 >= (int64_t(16) << 20);
+  if (!trace && loop_env != 0 && (!best.kern || (best_waves > 1 && (large || loop_env == 1)))) {
+    int cpw = 0;
+    GemvKernel k = loop_kernel_for(bits, mh, gps, xc, &cpw);
+    static const int kq_order[] = {4, 8, 2, 16, 1};
+    for (int kq : kq_order) {
+      if (!k || steps % (kq * cpw)) continue;
+      GemvSplit sp;
+      sp.KQ = kq;
+      sp.CPW = cpw;
+      sp.kern = k;
+      sp.R = steps / (kq * cpw);
+      return sp;
     }
   }
   return best;
@@ -519,6 +579,7 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
     const GemvSplit& sp = split[mb <= 2 ? 0 : (mb <= 8 ? 1 : 2)];
     p.KQ = sp.KQ;
     p.CPW = sp.CPW;
+    p.R = sp.R;
     const int rc = launch_gemv(sp, p, stream);
     if (rc) return rc;
   }

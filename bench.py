@@ -398,6 +398,49 @@ class DecodeSweepConfig3(Workload):
 WORKLOADS = {"c1": W4A16Config1, "c2": W4A4Config2, "c3": DecodeSweepConfig3}
 
 
+def library_gemm_same_shape(device, m, k, n, kind, reps=40):
+    """Context for a tensor-bound roofline: the vendor library's plain dense GEMM on this very shape,
+    timed by the protocol of the bench (one kernel per CUDA graph, graphs replayed back to back over
+    rotating operands).  ``kind`` "f16": torch.matmul on fp16 operands (what the reference's
+    dequantize-then-matmul path runs after its dequantisation); "int8": torch._int_mm.  Not a peak and
+    not this library's code: a 20-50 us problem does not reach the 8192^3 rate in any implementation."""
+    try:
+        nset = 6
+        if kind == "f16":
+            a = [torch.randn(m, k, device=device).half() for _ in range(nset)]
+            b = [torch.randn(n, k, device=device).half().t() for _ in range(nset)]
+            fn = lambda i: torch.matmul(a[i], b[i])
+        else:
+            a = [torch.randint(-8, 8, (m, k), dtype=torch.int8, device=device) for _ in range(nset)]
+            b = [torch.randint(-8, 8, (n, k), dtype=torch.int8, device=device).t() for _ in range(nset)]
+            fn = lambda i: torch._int_mm(a[i], b[i])
+        st = torch.cuda.Stream(device)
+        graphs = []
+        with torch.cuda.stream(st):
+            for i in range(nset):
+                fn(i)
+                torch.cuda.synchronize(device)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    fn(i)
+                graphs.append(g)
+            for g in graphs:
+                g.replay()
+            torch.cuda.synchronize(device)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for r in range(reps):
+                graphs[r % nset].replay()
+            e1.record(st)
+            torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / reps
+        return {"ms": ms, "rate": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+                "what": ("torch.matmul fp16" if kind == "f16" else "torch._int_mm int8") +
+                        f" {m}x{n}x{k}, dense operands, no dequantisation or group scales, same graph-replay protocol"}
+    except Exception as e:
+        return {"error": repr(e)}
+
+
 def time_int8_peak(device):
     """Dense int8 tensor throughput of this GPU (library GEMM), used only as a roofline denominator."""
     try:
@@ -600,6 +643,11 @@ def main():
     }
     if rank == 0:
         line["roofline"] = wl.roofline(kernel_ms, peaks, int8_tops)
+        if wl.name == "c1":
+            line["roofline"]["library_gemm_same_shape"] = library_gemm_same_shape(device, wl.M, wl.K, wl.N, "f16")
+        elif wl.name == "c2":
+            line["roofline"]["library_gemm_same_shape"] = library_gemm_same_shape(device, wl.M, wl.K, wl.N, "int8")
+            line["roofline"]["library_f16_gemm_same_shape"] = library_gemm_same_shape(device, wl.M, wl.K, wl.N, "f16")
         line["e2e"] = e2e
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl)

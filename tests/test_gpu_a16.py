@@ -78,6 +78,33 @@ def test_gemv_edge_shapes(bits, g, m, k, n, bias):
     assert_close_rows(y, _ref32(case), what=f"gemv edge w{bits} g{g} m{m} {k}x{n}")
 
 
+@pytest.mark.parametrize("bits,g,m,k,n,bias,dtype", [
+    (4, 128, 1, 16384, 256, False, torch.float16),    # K beyond 16 warps x 4 steps: 8 rounds per warp
+    (4, 64, 5, 16384, 128, True, torch.float16),
+    (4, 32, 16, 8192, 64, False, torch.float16),      # four groups per step: two steps per round
+    (2, 64, 2, 32768, 64, True, torch.float16),
+    (2, 256, 20, 16384, 128, False, torch.bfloat16),  # two launches (16 + 4 tokens)
+    (4, 128, 3, 8192, 4096, False, torch.float16),    # 16 MiB of weights: more than one resident wave
+])
+def test_gemv_rounds(bits, g, m, k, n, bias, dtype):
+    """Long K and large layers run on small blocks whose warps walk K in rounds."""
+    gen = torch.Generator().manual_seed(bits * 13 + m)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen).to(dtype), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half() if bias else None,
+                bits=bits, group_size=g)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemv", case, dtype=dtype)
+    ref = _ref32(case, dtype)
+    extra = bf16_half_ulp(ref) if dtype == torch.bfloat16 else None
+    if extra is None:
+        assert_close_rows(y, ref, what=f"gemv rounds w{bits} g{g} m{m} {k}x{n}")
+    else:
+        assert_close_rows(y, ref, rel=2e-3, extra=extra, what=f"gemv rounds bf16 w{bits} g{g} m{m} {k}x{n}")
+    y2 = run_a16_abi(f"asrq_w{bits}a16_gemv", case, dtype=dtype)
+    assert torch.equal(y, y2)
+
+
 def test_gemv_deterministic_and_workspace_clean():
     """Split-K partial sums are added in slice order: repeated runs are bit-identical."""
     case = O.make_c3(seed=7, m=4, k=6144, n=2048, bits=4, group_size=64)
