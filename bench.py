@@ -395,7 +395,73 @@ class DecodeSweepConfig3(Workload):
         return run, float(b), "one launch of the sweep: W4 g64 K=2048 N=6144 M=1, dequantize + torch.matmul"
 
 
-WORKLOADS = {"c1": W4A16Config1, "c2": W4A4Config2, "c3": DecodeSweepConfig3}
+class DecodeLargeLayer(Workload):
+    """Supplementary, not a BASELINE config: the decode kernel on one layer large enough that launch and
+    ramp-up latency do not dominate (W4 g128, 8192 -> 28672, M=1; 112 MiB of packed weights per launch)."""
+    name = "large"
+    metric = "linearq_decode_gemv_bandwidth_large_layer"
+    unit = "GB/s"
+    dtype = "f16 (fp32 accumulation)"
+    M, K, N, G = 1, 8192, 28672, 128
+    launches_per_step = 1
+
+    def __init__(self, device, seed):
+        from asrq_b200 import _lib
+        self.lib, self.dev = _lib, device
+        gen = torch.Generator(device=device).manual_seed(seed)
+        # timing only (parity of this kernel variant is a test): random packed bytes, positive scales
+        self.ws_ = [torch.randint(0, 256, (self.N, self.K // 2), dtype=torch.uint8, device=device, generator=gen)
+                    for _ in range(3)]
+        self.s = (torch.rand(self.N, self.K // self.G, device=device, generator=gen) * 0.01 + 0.001).half()
+        self.z = (torch.rand(self.N, self.K // self.G, device=device, generator=gen) * -0.05).half()
+        self.x = torch.randn(self.M, self.K, device=device, generator=gen).half()
+        self.y = torch.empty(self.M, self.N, dtype=torch.float16, device=device)
+        self.ws = torch.zeros(max(1 << 20, _lib.workspace_bytes(_lib.WS_LINEARQ, self.M, self.N, self.K)),
+                              dtype=torch.uint8, device=device)
+        self.l2_note = "rotating 3 weight copies (336 MiB > 126 MiB L2)"
+
+    nsets = 3
+    kernels = ["gemv_a16"]
+
+    def units_per_step(self):
+        return float(2 * self.M * self.K + self.N * self.K // 2 + 2 * self.N * (self.K // self.G) * 2 + 2 * self.M * self.N)
+
+    def run_kernel(self, name, i):
+        self.lib.call("asrq_w4a16_gemv", self.x.data_ptr(), self.ws_[i % 3].data_ptr(), self.s.data_ptr(),
+                      self.z.data_ptr(), None, self.y.data_ptr(), self.M, self.N, self.K, self.G, self.lib.F16,
+                      self.ws.data_ptr(), self.ws.numel(), torch.cuda.current_stream().cuda_stream)
+
+    def step(self, i):
+        self.run_kernel("gemv_a16", i)
+
+    def e2e_step(self, i):
+        if not hasattr(self, "x_host"):
+            self.x_host = self.x.cpu().pin_memory()
+            self.y_host = torch.empty(self.M, self.N, dtype=torch.float16).pin_memory()
+        xd = self.x_host.to(self.dev, non_blocking=True)
+        self.lib.call("asrq_w4a16_gemv", xd.data_ptr(), self.ws_[i % 3].data_ptr(), self.s.data_ptr(),
+                      self.z.data_ptr(), None, self.y.data_ptr(), self.M, self.N, self.K, self.G, self.lib.F16,
+                      self.ws.data_ptr(), self.ws.numel(), torch.cuda.current_stream().cuda_stream)
+        self.y_host.copy_(self.y, non_blocking=True)
+        return self.x_host.numel() * 2, self.y_host.numel() * 2
+
+    def cpu_sample(self):
+        from oracle import linearq_oracle as O
+        rows = 1024
+        c = O.make_c3(seed=0, m=1, k=self.K, n=rows, bits=4, group_size=self.G)
+
+        def run():
+            return O.linearq_forward(c["x"].float(), c["weight"], c["scales"], c["zeros"], None, 4, self.G)
+        b = 2 * self.K + rows * self.K // 2 + 2 * rows * (self.K // self.G) * 2 + 2 * rows
+        return run, float(b), f"{rows} of {self.N} output features, full K, M=1: dequantize + torch.matmul"
+
+    def roofline(self, kernel_ms, peaks, int8_tops):
+        ach = self.units_per_step() / (kernel_ms["gemv_a16"] * 1e-3) / 1e9
+        return {"kernel": "gemv_a16 (rounds variant)", "bound": "hbm", "achieved": ach, "unit": "GB/s",
+                "peak": peaks["hbm_gbs"], "frac": ach / peaks["hbm_gbs"], "of": peaks["source"], "traffic": None}
+
+
+WORKLOADS = {"c1": W4A16Config1, "c2": W4A4Config2, "c3": DecodeSweepConfig3, "large": DecodeLargeLayer}
 
 
 def library_gemm_same_shape(device, m, k, n, kind, reps=40):
@@ -490,7 +556,7 @@ def run_reference(args, rank):
         wl.case = O.make_c2(seed=args.seed, m=512, k=cls.K, n=cls.N, group_size=cls.G)
     elif args.workload == "c1":
         wl.case = O.make_c1(seed=args.seed, m=cls.M, k=cls.K, n=cls.N, bits=4, group_size=cls.G)
-    else:
+    elif args.workload == "c3":
         wl.case0 = O.make_c3(seed=args.seed, m=1, k=2048, n=6144, bits=4, group_size=cls.G)
     run, units, sample = wl.cpu_sample()
     torch.set_num_threads(os.cpu_count() or 1)
@@ -664,6 +730,8 @@ def main():
                 also.append({"workload": other, "metric": w2.metric, "value": w2.units_per_step() / (ms2 * 1e-3) / sc2,
                              "unit": w2.unit, "ms_per_step": ms2, "kernel_ms": k2,
                              "roofline": w2.roofline(k2, peaks, None)})
+                if other == "c1":
+                    also[-1]["roofline"]["library_gemm_same_shape"] = library_gemm_same_shape(device, w2.M, w2.K, w2.N, "f16")
                 del w2
                 torch.cuda.empty_cache()
             except Exception as e:  # a secondary row must not take the headline down

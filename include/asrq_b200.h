@@ -58,9 +58,10 @@ extern "C" {
 
 /*
  * Bytes of scratch the caller must pass as `workspace` for one call of the
- * given kind and shape.  The first 256 bytes of every workspace are a status
- * block that must be zero before the first use (cudaMemset once); the kernels
- * keep it consistent afterwards.  Counterpart of mymatmul_workspace_sizes
+ * given kind and shape.  The first 16640 bytes of every workspace (a 256-byte
+ * status block, then 4096 tile counters where the workspace is that large) must
+ * be zero before the first use (cudaMemset once); the kernels leave them zero
+ * after every call that completes.  Counterpart of mymatmul_workspace_sizes
  * (asrq/matmulq/csrc/bindings.cpp:17-22,192-198), which sized the reference's
  * stream-K workspace and lock array.
  */
@@ -101,7 +102,11 @@ int asrq_w4a16_gemv_static(const void* x, const uint8_t* w, const void* scales, 
  * Same contraction for large M (the prefill / encoder path): weights are unpacked
  * and scaled in registers, staged to shared memory and fed to tcgen05 kind::f16
  * MMAs with TMEM accumulators; activations arrive by TMA.
- * Requires N % 128 == 0, K % 64 == 0, group_size % 64 == 0, K % group_size == 0.
+ * Requires M >= 32, N % 128 == 0, K % 64 == 0, group_size % 64 == 0, K % group_size == 0.
+ * For M <= 256 the K range of an output tile may be divided among several blocks
+ * (fp32 parts in the workspace, added in a fixed order); with a workspace smaller
+ * than asrq_workspace_bytes(ASRQ_WS_A16_GEMM, M, N, K) but at least 256 bytes the
+ * call still runs, unsplit.
  * Replaces matmul_f16xint4 / matmul_f16xint2 for M > 64
  * (asrq/matmulq/csrc/bindings.cpp:44-57, 607-650, 705-747).
  */
