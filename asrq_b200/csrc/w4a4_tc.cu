@@ -92,6 +92,11 @@ struct W4A4TcParams {
 
 constexpr int kW4A4MaxBufs = 4;
 constexpr int kW4A4MaxStages = 8;
+// The CTA-pair kernel is parity-green but measured 1.8-2x slower than one CTA per tile on M=6000 K=4096
+// N=1024 at every tile width tried (78 against 44 us at BT=192), also with one barrier arrival per drain
+// warp instead of per thread and with every CTA's loads completing on its own barrier (a relay thread
+// forwards "landed" to CTA 0 once per stage) instead of on the peer's: it runs only on request.
+constexpr bool kW4A4PairDefault = false;
 constexpr int w4a4_threads(int cg) { return 32 * (4 + 4 * cg); }  // producer, two MMA issuers, one idle, drain
 constexpr uint32_t kW8TileBytes = 128 * 128;
 
@@ -99,18 +104,25 @@ constexpr uint32_t kW8TileBytes = 128 * 128;
 // F8 = true: operands are e4m3 bytes holding the code, kind::f8f6f4, fp32 sums in TMEM: a group sum is
 // an integer of magnitude <= 128 * 64, so it is exact, and the drain needs no int->float conversion.
 // CG: column groups of the drain (4 * CG drain warps); NCH: 16-column chunks a drain warp handles at most.
-template <bool DUMP, bool F8, int CG, int NCH>
-__global__ void __launch_bounds__(w4a4_threads(CG), 1)
-w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tma,
-               const W4A4TcParams p) {
+// PAIR: two CTAs of a cluster work on one 256-feature x BT-token tile with tcgen05 cta_group::2 MMAs.
+// Each CTA loads its own 128 weight rows and HALF of the activation rows of a K block (the MMA reads
+// the other half from the peer's shared memory), which cuts the bytes an SM takes in per MMA cycle
+// from 16 KB + BT*128 to 16 KB + BT*64 per K block.  CTA 0 issues for both, its full[] barriers count
+// the bytes of both CTAs' loads, commits are multicast to both CTAs' empty[]/accf[] barriers, and the
+// drain warps of both CTAs arrive on CTA 0's acce[] barriers.
+template <bool DUMP, bool F8, int CG, int NCH, bool PAIR>
+__device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUtensorMap* tma_p, const W4A4TcParams& p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kW4A4MaxStages + 2 * kW4A4MaxBufs];
+  __shared__ __align__(8) uint64_t bars[3 * kW4A4MaxStages + 2 * kW4A4MaxBufs];
   __shared__ uint32_t tmem_slot;
 
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
-  const uint32_t bbytes = uint32_t(p.bt) * 128u;
+  const uint32_t bbytes = uint32_t(PAIR ? p.bt / 2 : p.bt) * 128u;  // this CTA's activation rows of a K block
   const uint32_t stage_bytes = kW8TileBytes + bbytes;
+  const uint32_t rank = PAIR ? tc::cluster_ctarank() : 0u;
+  const int worker = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);     // tile-loop start and stride:
+  const int nworkers = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);     // CTAs, or CTA pairs
   const int nst = p.nstages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = tc::smem_u32(bars);
@@ -118,31 +130,42 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
   auto empty_bar = [&](int s) { return bar0 + 8u * (kW4A4MaxStages + s); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + b); };
   auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kW4A4MaxStages + kW4A4MaxBufs + b); };
+  // PAIR, CTA 0: "the peer's tiles of stage s have landed" (one remote arrival per stage by the peer's relay thread)
+  auto pfull_bar = [&](int s) { return bar0 + 8u * (2 * kW4A4MaxStages + 2 * kW4A4MaxBufs + s); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
       tc::mbar_init(full_bar(s), 1);
       tc::mbar_init(empty_bar(s), 1);
+      tc::mbar_init(pfull_bar(s), 1);
     }
     for (int b = 0; b < p.nbuf; ++b) {
       tc::mbar_init(accf_bar(b), 1);
-      tc::mbar_init(acce_bar(b), 32 * 4 * CG);
+      tc::mbar_init(acce_bar(b), PAIR ? 2 * 4 * CG : 32 * 4 * CG);  // per drain warp of both CTAs / per drain thread
     }
     tc::fence_barrier_init();
     tc::fence_proxy_async_smem();
-    tc::prefetch_tmap(&tmw);
-    tc::prefetch_tmap(&tma);
+    tc::prefetch_tmap(tmw_p);
+    tc::prefetch_tmap(tma_p);
   }
   if (warp == 1) {
-    tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
-    tc::tmem_relinquish();
+    if (PAIR) {
+      tc::tmem_alloc_pair(tc::smem_u32(&tmem_slot), 512);
+      tc::tmem_relinquish_pair();
+    } else {
+      tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
+      tc::tmem_relinquish();
+    }
   }
   tc::fence_before_sync();
   __syncthreads();
+  if (PAIR) tc::cluster_sync();  // the peer's barriers are initialised before anything arrives on them
   tc::fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
 
-  const int ntiles = p.n_ftiles * p.n_ttiles;
+  // PAIR: a "tile" is the feature-tile pair (2j, 2j+1) of a token tile; this CTA owns feature tile 2j + rank
+  const int n_ft = PAIR ? p.n_ftiles / 2 : p.n_ftiles;
+  const int ntiles = n_ft * p.n_ttiles;
   const int nkb = p.K / 128;
   const bool tr = p.trace != nullptr && blockIdx.x == 0;
   auto mark = [&](int role, uint32_t i, int slot) {
@@ -155,16 +178,18 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
       uint32_t it = 0, ph = 0;
       int s = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
-        const int row_w = ft * 128, row_a = tt * p.bt;
+      for (int tile = worker; tile < ntiles && ok; tile += nworkers) {
+        const int ft = PAIR ? 2 * (tile % n_ft) + int(rank) : tile % n_ft, tt = tile / n_ft;
+        const int row_w = ft * 128, row_a = tt * p.bt + (PAIR ? int(rank) * (p.bt / 2) : 0);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11)) { ok = false; break; }
           mark(0, it, 0);
           const uint32_t sb = base + s * stage_bytes;
+          // every CTA's loads complete on its own barrier (a load that counts its bytes on the peer's
+          // barrier measured far slower); the peer's relay thread forwards "landed" once per stage
           tc::mbar_arrive_expect_tx(full_bar(s), kW8TileBytes + bbytes);
-          tc::tma_load_2d(sb, &tmw, kb * 128, row_w, full_bar(s));
-          tc::tma_load_2d(sb + kW8TileBytes, &tma, kb * 128, row_a, full_bar(s));
+          tc::tma_load_2d(sb, tmw_p, kb * 128, row_w, full_bar(s));
+          tc::tma_load_2d(sb + kW8TileBytes, tma_p, kb * 128, row_a, full_bar(s));
           mark(0, it, 1);
           if (++s == nst) { s = 0; ph ^= 1u; }
         }
@@ -177,19 +202,24 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
     // so issuer w-1 takes the groups that land in buffer w-1: the two threads never touch the same
     // accumulator, each commit tracks only its own thread's MMAs, and shared-memory stages are
     // consumed independently, so they need no ordering between them.
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       const uint32_t me = uint32_t(warp - 1);
-      const uint32_t idesc = F8 ? tc::instr_desc(1u, 0u, 128u, uint32_t(p.bt)) : tc::instr_desc(2u, 1u, 128u, uint32_t(p.bt));
+      const uint32_t mrows = PAIR ? 256u : 128u;
+      const uint32_t idesc = F8 ? tc::instr_desc(1u, 0u, mrows, uint32_t(p.bt)) : tc::instr_desc(2u, 1u, mrows, uint32_t(p.bt));
       uint32_t it = 0, ac = 0, ph = 0;  // K block, group and stage phase, counted over ALL groups
       uint32_t buf = 0, bph = 0;        // accumulator buffer of group ac and the parity of its use count
       int s = 0, gb = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < ntiles && ok; tile += nworkers) {
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           // Both issuers observe every phase of every stage barrier, also for the other one's K blocks:
           // a waiter that skipped a phase could mistake an older, still incomplete phase of the same
           // parity for the one it wants.  (Accumulator buffers never change hands: their number is even.)
           ok = tc::mbar_wait_spin(full_bar(s), ph, p.status, 13);
+          if (PAIR && ok) {
+            ok = tc::mbar_wait_spin(pfull_bar(s), ph, p.status, 15);
+            asm volatile("fence.acq_rel.cluster;" ::: "memory");
+          }
           if (!ok) break;
           if ((ac & 1u) == me) {
             if (gb == 0) {  // fresh accumulator: its previous contents must have been drained
@@ -202,7 +232,12 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
             const uint32_t d_tmem = tmem_base + buf * uint32_t(p.bt);
             // a K step of 32 bytes = +2 in the descriptor's 16-byte address field
             const uint64_t da = tc::smem_desc_sw128(sb), db = tc::smem_desc_sw128(sb + kW8TileBytes);
-            if (F8) {
+            if (PAIR) {
+              tc::mma_8bit_pair<F8>(d_tmem, da, db, idesc, uint32_t(gb != 0));
+              tc::mma_8bit_pair<F8>(d_tmem, da + 2, db + 2, idesc, 1u);
+              tc::mma_8bit_pair<F8>(d_tmem, da + 4, db + 4, idesc, 1u);
+              tc::mma_8bit_pair<F8>(d_tmem, da + 6, db + 6, idesc, 1u);
+            } else if (F8) {
               tc::mma_f8(d_tmem, da, db, idesc, uint32_t(gb != 0));
               tc::mma_f8(d_tmem, da + 2, db + 2, idesc, 1u);
               tc::mma_f8(d_tmem, da + 4, db + 4, idesc, 1u);
@@ -213,8 +248,13 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
               tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
               tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
             }
-            tc::mma_commit(empty_bar(s));
-            if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(buf));
+            if (PAIR) {
+              tc::mma_commit_pair(empty_bar(s), 3);
+              if (gb + 1 == p.blocks_per_group) tc::mma_commit_pair(accf_bar(buf), 3);
+            } else {
+              tc::mma_commit(empty_bar(s));
+              if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(buf));
+            }
           }
           if (++s == nst) { s = 0; ph ^= 1u; }
           if (++gb == p.blocks_per_group) {
@@ -225,6 +265,21 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
         }
       }
     }
+  } else if (warp == 3) {
+    // PAIR, CTA 1: relay.  Waits for each stage of this CTA to land and tells CTA 0's issuers.
+    if (PAIR && rank == 1 && lane == 0) {
+      const uint32_t pfull0 = tc::mapa(pfull_bar(0), 0);
+      uint32_t ph = 0;
+      int s = 0;
+      bool ok = true;
+      for (int tile = worker; tile < ntiles && ok; tile += nworkers) {
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!tc::mbar_wait(full_bar(s), ph, p.status, 16)) { ok = false; break; }
+          tc::mbar_arrive_cluster(pfull0 + 8u * s);
+          if (++s == nst) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
   } else if (warp >= 4) {
     const int qd = warp & 3;           // TMEM lane quadrant this warp may read
     const int cg = (warp - 4) >> 2;    // column group 0..2
@@ -232,8 +287,8 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
     const int nch = wcols >> 4;        // 16-column chunks: 1..NCH
     uint32_t ac = 0, buf = 0, aph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      const int ft = tile % p.n_ftiles, tt = tile / p.n_ftiles;
+    for (int tile = worker; tile < ntiles && ok; tile += nworkers) {
+      const int ft = PAIR ? 2 * (tile % n_ft) + int(rank) : tile % n_ft, tt = tile / n_ft;
       const int f = ft * 128 + qd * 32 + lane;
       const __half* swrow = p.sw + size_t(f) * p.groups;
       float2 accf[8 * NCH];  // running fp32 sums, two columns per register pair (packed fp32 FMA)
@@ -257,8 +312,20 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
             if (ch + 1 < nch) {
               tc::tmem_ld_32x16(taddr + (ch + 1) * 16, r[(ch + 1) & 1]);
             } else {  // buffer fully read: hand it back before the math
+              // PAIR: one arrival per warp (an arrival from the peer CTA is a remote shared-memory operation)
               tc::fence_before_sync();
-              tc::mbar_arrive(acce_bar(buf));
+              if (PAIR) {
+                __syncwarp();
+                if (lane == 0) {
+                  if (rank != 0) {
+                    tc::mbar_arrive_cluster(tc::mapa(acce_bar(buf), 0));
+                  } else {
+                    tc::mbar_arrive(acce_bar(buf));
+                  }
+                }
+              } else {
+                tc::mbar_arrive(acce_bar(buf));
+              }
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -298,10 +365,28 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
   __syncwarp();
   tc::fence_before_sync();
   __syncthreads();
+  if (PAIR) tc::cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its memory
   if (warp == 1) {
     tc::fence_after_sync();
-    tc::tmem_dealloc(tmem_base, 512);
+    if (PAIR) {
+      tc::tmem_dealloc_pair(tmem_base, 512);
+    } else {
+      tc::tmem_dealloc(tmem_base, 512);
+    }
   }
+}
+
+template <bool DUMP, bool F8, int CG, int NCH>
+__global__ void __launch_bounds__(w4a4_threads(CG), 1)
+w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tma,
+               const W4A4TcParams p) {
+  w4a4_tc_body<DUMP, F8, CG, NCH, false>(&tmw, &tma, p);
+}
+template <bool DUMP, bool F8, int CG, int NCH>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(w4a4_threads(CG), 1)
+w4a4_tc_pair_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tma,
+                    const W4A4TcParams p) {
+  w4a4_tc_body<DUMP, F8, CG, NCH, true>(&tmw, &tma, p);
 }
 
 // Token-tile width.  Two drain geometries: three column groups (BT a multiple of 48, up to 192, up to
@@ -310,6 +395,7 @@ w4a4_tc_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ 
 struct W4A4Tile {
   int bt, cg;
 };
+// `N` and `sm_count` are halved by the caller for the CTA-pair kernel (feature-tile pairs over CTA pairs).
 static W4A4Tile w4a4_pick_tile(int64_t M, int64_t N, int sm_count) {
   static const int bt_env = getenv("ASRQ_B200_W4A4_BT") ? atoi(getenv("ASRQ_B200_W4A4_BT")) : 0;  // tuning knob
   if (bt_env > 0 && bt_env <= 192 && (bt_env % 48 == 0 || bt_env % 64 == 0))
@@ -370,13 +456,18 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   p.K = int(K);
   p.groups = int(K / group_size);
   p.blocks_per_group = group_size / 128;
-  const W4A4Tile tile = w4a4_pick_tile(M, N, sm_count);
+  // CTA pairs (tcgen05 cta_group::2) halve the activation bytes an SM takes in per MMA; they need an even
+  // number of feature tiles.  ASRQ_B200_W4A4_PAIR=0 / 1 forces the choice (tuning knob).
+  const char* pair_str = getenv("ASRQ_B200_W4A4_PAIR");
+  const int pair_env = pair_str ? atoi(pair_str) : -1;
+  const bool pair = (N / 128) % 2 == 0 && sm_count >= 2 && pair_env != 0 && (pair_env == 1 || kW4A4PairDefault);
+  const W4A4Tile tile = pair ? w4a4_pick_tile(M, N / 2, sm_count / 2) : w4a4_pick_tile(M, N, sm_count);
   p.bt = tile.bt;
   p.nbuf = 512 / p.bt >= 4 ? 4 : 2;  // even, so that a buffer always belongs to the same issuer
   p.n_ftiles = int(N / 128);
   p.n_ttiles = int((M + p.bt - 1) / p.bt);
   p.bf16 = dtype == ASRQ_BF16;
-  const size_t stage_bytes = kW8TileBytes + size_t(p.bt) * 128;
+  const size_t stage_bytes = kW8TileBytes + size_t(pair ? p.bt / 2 : p.bt) * 128;
   const size_t budget = 227 * 1024 - 1024 - 512;
   p.nstages = int(std::min<size_t>(kW4A4MaxStages, budget / stage_bytes));
   const size_t smem = 1024 + p.nstages * stage_bytes;
@@ -384,11 +475,19 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   CUtensorMap tmw, tma;
   int rc = make_tmap_2d(&tmw, w8, 1, false, uint64_t(K), uint64_t(N), 128, 128, true);
   if (rc) return rc;
-  rc = make_tmap_2d(&tma, a8, 1, false, uint64_t(K), uint64_t(M), 128, uint32_t(p.bt), true);
+  rc = make_tmap_2d(&tma, a8, 1, false, uint64_t(K), uint64_t(M), 128, uint32_t(pair ? p.bt / 2 : p.bt), true);
   if (rc) return rc;
-  const int grid = int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles, sm_count));
+  const int grid = pair ? 2 * int(std::min<int64_t>(int64_t(p.n_ftiles / 2) * p.n_ttiles, sm_count / 2))
+                        : int(std::min<int64_t>(int64_t(p.n_ftiles) * p.n_ttiles, sm_count));
   void (*kern)(const CUtensorMap, const CUtensorMap, const W4A4TcParams);
-  if (tile.cg == 3)
+  if (pair) {
+    if (tile.cg == 3)
+      kern = fmt == 2 ? (acc_dump ? w4a4_tc_pair_kernel<true, true, 3, 4> : w4a4_tc_pair_kernel<false, true, 3, 4>)
+                      : (acc_dump ? w4a4_tc_pair_kernel<true, false, 3, 4> : w4a4_tc_pair_kernel<false, false, 3, 4>);
+    else
+      kern = fmt == 2 ? (acc_dump ? w4a4_tc_pair_kernel<true, true, 4, 2> : w4a4_tc_pair_kernel<false, true, 4, 2>)
+                      : (acc_dump ? w4a4_tc_pair_kernel<true, false, 4, 2> : w4a4_tc_pair_kernel<false, false, 4, 2>);
+  } else if (tile.cg == 3)
     kern = fmt == 2 ? (acc_dump ? w4a4_tc_kernel<true, true, 3, 4> : w4a4_tc_kernel<false, true, 3, 4>)
                     : (acc_dump ? w4a4_tc_kernel<true, false, 3, 4> : w4a4_tc_kernel<false, false, 3, 4>);
   else

@@ -183,6 +183,29 @@ def test_w4a4_gemm_exact_accumulators_and_output(m, k, n, g, bias):
     assert torch.equal(qf.cpu(), qa_ref.float()) and torch.equal(sf.cpu().reshape(-1), sa_ref)
 
 
+@pytest.mark.parametrize("m,k,n", [(333, 4096, 1024), (100, 512, 256), (700, 1024, 512)])
+def test_w4a4_cta_pair_variant(m, k, n, monkeypatch):
+    """The opt-in CTA-pair kernel (tcgen05 cta_group::2): the same integer group sums and output bits."""
+    g = 128
+    x, w, b = _w4a4_case(m, k, n, g, seed=m + k + 1, bias=True)
+    qa_ref, sa_ref, _ = O.hadamard_quant_int4(x, True)
+    codes, sw, _ = O.prepare_w4a4_weight(w, g, True)
+    acc_ref = O.int4_group_accumulators(qa_ref, codes, g)
+    lq = asrq_b200.LinearQQ(k, n, 4, 4, g, bias=True, hadamard=True).to(DEV)
+    pw2, sw2 = asrq_b200.pack_w4a4(w, g, True)
+    lq.load_quantized_params(sw2, torch.zeros_like(sw2), pw2)
+    lq.bias = b.to(DEV)
+    y_single = lq(x.to(DEV))
+    monkeypatch.setenv("ASRQ_B200_W4A4_PAIR", "1")
+    acc = torch.full((m, n, k // g), -12345, dtype=torch.int32, device=DEV)
+    y_pair = lq(x.to(DEV), acc_dump=acc)
+    asrq_b200.check_status()
+    assert torch.equal(acc.cpu(), acc_ref), "int32 group accumulators differ (pair kernel)"
+    assert torch.equal(y_pair, y_single)
+    lq.operand = "int8" if lq.operand == "f8" else "f8"
+    assert torch.equal(lq(x.to(DEV)), y_single)
+
+
 def test_w4a4_tracks_unquantised_product():
     """End-to-end sanity at config-2 widths: the rotation cancels and 4x4-bit error stays moderate."""
     x, w, b = _w4a4_case(128, 4096, 1024, 128, seed=9, bias=False)
