@@ -287,7 +287,7 @@ class W4A16Config1(Workload):
                 "peak": peaks["bf16_tflops"], "frac": ach / peaks["bf16_tflops"], "of": peaks["source"] + " (burst)",
                 # dram bytes of one gemm_a16_tc_kernel launch from the ncu capture summarised in
                 # profiles/gemm_a16_tc_c1.md (x and W are L2 hits after the first touch, y was still in L2)
-                "traffic": 7364352, "traffic_algorithmic": 22691840}
+                "traffic": 7385856, "traffic_algorithmic": 22691840}
 
     def cpu_sample(self):
         from oracle import linearq_oracle as O
@@ -380,10 +380,10 @@ class DecodeSweepConfig3(Workload):
         ach = self.total_bytes / (kernel_ms["gemv_a16 (30 launches)"] * 1e-3) / 1e9
         return {"kernel": "gemv_a16", "bound": "hbm", "achieved": ach, "unit": "GB/s", "peak": peaks["hbm_gbs"],
                 "frac": ach / peaks["hbm_gbs"], "of": peaks["source"],
-                # ncu captured one launch of the sweep (W4 2048->6144, M=1): 7 096 832 B of DRAM reads for
+                # ncu captured one launch of the sweep (W4 2048->6144, M=1): 7 101 440 B of DRAM reads for
                 # 7 094 272 algorithmic bytes (profiles/gemv_a16_c3.md); the sweep's traffic is its algorithmic
                 # bytes scaled by that ratio (every launch streams its weights exactly once)
-                "traffic": self.total_bytes * 7096832.0 / 7094272.0}
+                "traffic": self.total_bytes * 7101440.0 / 7094272.0}
 
     def cpu_sample(self):
         from oracle import linearq_oracle as O
