@@ -267,6 +267,10 @@ template <int OUT, bool BF16>
 __global__ void __launch_bounds__(kHad4096Warps * 32, 3)
 hadamard4096_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ qa, float* __restrict__ sa, int M) {
   extern __shared__ uint4 smem4[];
+  // A GEMM launched behind this kernel with programmatic stream serialisation may be scheduled once
+  // every block of this grid has started, and set itself up on SMs the last wave leaves idle; it
+  // orders itself with griddepcontrol.wait before it touches this kernel's output.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x * kHad4096Warps + warp;
   if (token >= M) return;  // warp-uniform; only warp-level synchronisation below

@@ -162,6 +162,10 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
   if (PAIR) tc::cluster_sync();  // the peer's barriers are initialised before anything arrives on them
   tc::fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+  // Launched with programmatic stream serialisation: everything above (barriers, tensor memory,
+  // descriptor prefetch) may overlap the tail of the kernel before; the activation operand, the
+  // token scales and the output belong to this kernel only from here on.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // PAIR: a "tile" is the feature-tile pair (2j, 2j+1) of a token tile; this CTA owns feature tile 2j + rank
   const int n_ft = PAIR ? p.n_ftiles / 2 : p.n_ftiles;
@@ -494,8 +498,17 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
     kern = fmt == 2 ? (acc_dump ? w4a4_tc_kernel<true, true, 4, 2> : w4a4_tc_kernel<false, true, 4, 2>)
                     : (acc_dump ? w4a4_tc_kernel<true, false, 4, 2> : w4a4_tc_kernel<false, false, 4, 2>);
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
-  kern<<<grid, w4a4_threads(tile.cg), smem, stream>>>(tmw, tma, p);
-  ASRQ_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(w4a4_threads(tile.cg));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = getenv("ASRQ_B200_NO_PDL") ? 0 : 1;
+  ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmw, tma, p));
   return ASRQ_OK;
 }
 
