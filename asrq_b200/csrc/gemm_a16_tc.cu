@@ -134,6 +134,10 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+  // Launched with programmatic stream serialisation: the set-up above may overlap the tail of the
+  // kernel before; activations, workspace and output are touched only from here on.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int nkb = p.K / 64;
   const int nitems = p.n_ftiles * p.n_ttiles * p.ksplit;
@@ -462,8 +466,17 @@ static int launch_tc(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmT
                      cudaStream_t stream) {
   auto kern = gemm_a16_tc_kernel<BITS, BF16>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
-  kern<<<grid, kTcThreads, smem, stream>>>(tmx, tmw, p);
-  ASRQ_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = getenv("ASRQ_B200_NO_PDL") ? 0 : 1;
+  ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmx, tmw, p));
   return ASRQ_OK;
 }
 
