@@ -87,15 +87,16 @@ struct W4A4TcParams {
   int32_t* acc_dump;
   unsigned* status;
   long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
-  int M, N, K, groups, blocks_per_group, bt, nbuf, nstages, n_ftiles, n_ttiles, bf16;
+  int M, N, K, groups, blocks_per_group, bt, nbuf, nstages, n_ftiles, n_ttiles, bf16, trace_block;
 };
 
 constexpr int kW4A4MaxBufs = 4;
 constexpr int kW4A4MaxStages = 8;
-// The CTA-pair kernel is parity-green but measured 1.8-2x slower than one CTA per tile on M=6000 K=4096
-// N=1024 at every tile width tried (78 against 44 us at BT=192), also with one barrier arrival per drain
-// warp instead of per thread and with every CTA's loads completing on its own barrier (a relay thread
-// forwards "landed" to CTA 0 once per stage) instead of on the peer's: it runs only on request.
+// The CTA-pair kernel is parity-green and measures 10-15 % slower than one CTA per tile on M=6000 K=4096
+// N=1024 at every tile width tried (45.6 against 40.1 us at BT=192): both are paced by the round trip of
+// the two accumulator buffers, not by operand delivery.  It runs only on request.  (It was 1.8-2x
+// slower until the cross-CTA arrivals lost their release semantics: a release at cluster scope stalls
+// the arriving warp for ~1000 cycles, once per drain warp per group and once per stage in the relay.)
 constexpr bool kW4A4PairDefault = false;
 constexpr int w4a4_threads(int cg) { return 32 * (4 + 4 * cg); }  // producer, two MMA issuers, one idle, drain
 constexpr uint32_t kW8TileBytes = 128 * 128;
@@ -171,7 +172,7 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
   const int n_ft = PAIR ? p.n_ftiles / 2 : p.n_ftiles;
   const int ntiles = n_ft * p.n_ttiles;
   const int nkb = p.K / 128;
-  const bool tr = p.trace != nullptr && blockIdx.x == 0;
+  const bool tr = p.trace != nullptr && int(blockIdx.x) == p.trace_block;
   auto mark = [&](int role, uint32_t i, int slot) {
     if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
   };
@@ -222,7 +223,6 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
           ok = tc::mbar_wait_spin(full_bar(s), ph, p.status, 13);
           if (PAIR && ok) {
             ok = tc::mbar_wait_spin(pfull_bar(s), ph, p.status, 15);
-            asm volatile("fence.acq_rel.cluster;" ::: "memory");
           }
           if (!ok) break;
           if ((ac & 1u) == me) {
@@ -279,7 +279,7 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
       for (int tile = worker; tile < ntiles && ok; tile += nworkers) {
         for (int kb = 0; kb < nkb; ++kb) {
           if (!tc::mbar_wait(full_bar(s), ph, p.status, 16)) { ok = false; break; }
-          tc::mbar_arrive_cluster(pfull0 + 8u * s);
+          tc::mbar_arrive_cluster_relaxed(pfull0 + 8u * s);
           if (++s == nst) { s = 0; ph ^= 1u; }
         }
       }
@@ -322,7 +322,7 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
                 __syncwarp();
                 if (lane == 0) {
                   if (rank != 0) {
-                    tc::mbar_arrive_cluster(tc::mapa(acce_bar(buf), 0));
+                    tc::mbar_arrive_cluster_relaxed(tc::mapa(acce_bar(buf), 0));
                   } else {
                     tc::mbar_arrive(acce_bar(buf));
                   }
@@ -455,6 +455,7 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   p.trace = (getenv("ASRQ_B200_TRACE") && workspace_bytes >= (1u << 20) + 3 * 512 * 2 * 8)
                 ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20))
                 : nullptr;
+  p.trace_block = getenv("ASRQ_B200_TRACE_BLOCK") ? atoi(getenv("ASRQ_B200_TRACE_BLOCK")) : 0;
   p.M = int(M);
   p.N = int(N);
   p.K = int(K);
