@@ -488,9 +488,12 @@ int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, 
 int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
-  // The CTA-pair variant (gemm_a16_tc2.cu, tcgen05 cta_group::2) measured slower on the shapes tried
-  // (32.5 us against 25.2 us on M=1500 K=1280 N=5120) and runs only on request.
-  if (getenv("ASRQ_B200_TC_PAIR") && gemm_a16_tc2_supports(M, N, K, group_size))
+  // The CTA-pair kernel (gemm_a16_tc2.cu, tcgen05 cta_group::2: half the activation rows per SM per
+  // MMA) takes large M where the shape allows (20.9 us against 23.1 us on M=1500 K=1280 N=5120); M <= 256
+  // stays here for the K split.  ASRQ_B200_TC_PAIR=1 / 0 forces / forbids it.
+  const char* pair_env = getenv("ASRQ_B200_TC_PAIR");
+  const bool want_pair = pair_env ? atoi(pair_env) != 0 : M > 256;
+  if (want_pair && gemm_a16_tc2_supports(M, N, K, group_size))
     return gemm_a16_tc2(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
                         sm_count, stream);
   if (N % 128 || K % 64 || group_size <= 0 || group_size % 64 || K % group_size)

@@ -79,12 +79,17 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   auto afree_bar = [&](int a) { return bar0 + 8u * (3 * kT2MaxStages + kT2Slots + a); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + b); };
   auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 2 + b); };
-  // arrive on a barrier of CTA 0 from either CTA
+  // One arrival per warp on a barrier of CTA 0, from either CTA, after every lane has made its writes
+  // visible to the async proxy.  The remote arrival is relaxed: with release semantics at cluster
+  // scope it stalls the arriving warp for ~1000 cycles.
   auto arrive_on_leader = [&](uint32_t bar) {
-    if (rank == 0) {
-      tc::mbar_arrive(bar);
-    } else {
-      tc::mbar_arrive_cluster(tc::mapa(bar, 0));
+    __syncwarp();
+    if (lane == 0) {
+      if (rank == 0) {
+        tc::mbar_arrive(bar);
+      } else {
+        tc::mbar_arrive_cluster_relaxed(tc::mapa(bar, 0));
+      }
     }
   };
 
@@ -95,12 +100,12 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
       tc::mbar_init(wfull_bar(s), 1);
     }
     for (int a = 0; a < kT2Slots; ++a) {
-      tc::mbar_init(deq_bar(a), 256);
+      tc::mbar_init(deq_bar(a), 8);  // four dequant warps of each CTA
       tc::mbar_init(afree_bar(a), 1);
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(accf_bar(b), 1);
-      tc::mbar_init(acce_bar(b), 256);
+      tc::mbar_init(acce_bar(b), 8);  // four epilogue warps of each CTA
     }
     tc::fence_barrier_init();
     tc::fence_proxy_async_smem();
@@ -144,7 +149,9 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
     }
   } else if (warp == kT2MmaWarp) {
     // ------------------------------ MMA issuer (CTA 0 only) ------------------------------
-    if (lane == 0 && rank == 0) {
+    // run by the whole warp (counters and descriptors stay warp-uniform), tcgen05 instructions under an elected lane
+    if (rank == 0) {
+      const bool el = tc::elect_one();
       const uint32_t idesc = tc::instr_desc(1u, BF16 ? 1u : 0u, 256u, uint32_t(p.bt));
       uint32_t ph = 0, dph = 0, ucount = 0;
       int s = 0, a = 0;
@@ -161,14 +168,16 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
           // a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address field
           const uint64_t da = tc::smem_desc_sw128(base + a * kT2ATileBytes);
           const uint64_t db = tc::smem_desc_sw128(base + a_ring_bytes + s * stage_bytes);
-          tc::mma_f16_pair(d_tmem, da, db, idesc, uint32_t(kb != 0));
-          tc::mma_f16_pair(d_tmem, da + 2, db + 2, idesc, 1u);
-          tc::mma_f16_pair(d_tmem, da + 4, db + 4, idesc, 1u);
-          tc::mma_f16_pair(d_tmem, da + 6, db + 6, idesc, 1u);
-          // frees the stage and the A slot in both CTAs
-          tc::mma_commit_pair(empty_bar(s), 3);
-          tc::mma_commit_pair(afree_bar(a), 3);
-          if (kb + 1 == nkb) tc::mma_commit_pair(accf_bar(buf), 3);
+          if (el) {
+            tc::mma_f16_pair(d_tmem, da, db, idesc, uint32_t(kb != 0));
+            tc::mma_f16_pair(d_tmem, da + 2, db + 2, idesc, 1u);
+            tc::mma_f16_pair(d_tmem, da + 4, db + 4, idesc, 1u);
+            tc::mma_f16_pair(d_tmem, da + 6, db + 6, idesc, 1u);
+            // frees the stage and the A slot in both CTAs
+            tc::mma_commit_pair(empty_bar(s), 3);
+            tc::mma_commit_pair(afree_bar(a), 3);
+            if (kb + 1 == nkb) tc::mma_commit_pair(accf_bar(buf), 3);
+          }
           if (++s == nst) { s = 0; ph ^= 1u; }
           if (++a == kT2Slots) { a = 0; dph ^= 1u; }
         }

@@ -243,7 +243,8 @@ def test_module_dispatch_and_leading_dims():
 
 @pytest.mark.parametrize("m,k,n,bits", [(64, 256, 256, 4), (300, 1280, 1024, 4), (1500, 1280, 5120, 4), (200, 1024, 512, 2)])
 def test_gemm_cta_pair_variant(m, k, n, bits, monkeypatch):
-    """The opt-in tcgen05 cta_group::2 kernel (two CTAs share one 256-row MMA) against the fp32 CPU result."""
+    """The tcgen05 cta_group::2 kernel (two CTAs share one 256-row MMA; the default for M > 256), forced
+    also for smaller M, against the fp32 CPU result."""
     monkeypatch.setenv("ASRQ_B200_TC_PAIR", "1")
     gen = torch.Generator().manual_seed(m + n)
     w = torch.randn(n, k, generator=gen) * 0.02
@@ -252,3 +253,19 @@ def test_gemm_cta_pair_variant(m, k, n, bits, monkeypatch):
                 zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half(), bits=bits, group_size=128)
     y = run_a16_abi(f"asrq_w{bits}a16_gemm", case)
     assert_close_rows(y, _ref32(case, torch.float16), what=f"pair gemm w{bits} m{m}")
+
+
+@pytest.mark.parametrize("m,k,n,bits", [(1500, 1280, 5120, 4), (6000, 1024, 4096, 4), (777, 6144, 2048, 2)])
+def test_gemm_single_cta_kernel_large_m(m, k, n, bits, monkeypatch):
+    """The one-CTA-per-tile kernel on large M (where the CTA-pair kernel is the default), and both agree."""
+    gen = torch.Generator().manual_seed(m + n + 5)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, 128, False)
+    case = dict(x=torch.randn(m, k, generator=gen).half(), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half(), bits=bits, group_size=128)
+    y_pair = run_a16_abi(f"asrq_w{bits}a16_gemm", case)
+    monkeypatch.setenv("ASRQ_B200_TC_PAIR", "0")
+    y_single = run_a16_abi(f"asrq_w{bits}a16_gemm", case)
+    ref = _ref32(case, torch.float16)
+    assert_close_rows(y_single, ref, what=f"single-CTA gemm w{bits} m{m}")
+    assert_close_rows(y_pair, ref, what=f"pair gemm w{bits} m{m}")
