@@ -283,11 +283,11 @@ class W4A16Config1(Workload):
 
     def roofline(self, kernel_ms, peaks, int8_tops):
         ach = self.units_per_step() / (kernel_ms["gemm_a16_tc"] * 1e-3) / 1e12
-        return {"kernel": "gemm_a16_tc", "bound": "tensor", "achieved": ach, "unit": "TFLOP/s",
+        return {"kernel": "gemm_a16_tc2 (CTA pairs)", "bound": "tensor", "achieved": ach, "unit": "TFLOP/s",
                 "peak": peaks["bf16_tflops"], "frac": ach / peaks["bf16_tflops"], "of": peaks["source"] + " (burst)",
-                # dram bytes of one gemm_a16_tc_kernel launch from the ncu capture summarised in
+                # dram bytes of one gemm_a16_tc2_kernel launch (the CTA-pair kernel) from the ncu capture summarised in
                 # profiles/gemm_a16_tc_c1.md (x and W are L2 hits after the first touch, y was still in L2)
-                "traffic": 7385856, "traffic_algorithmic": 22691840}
+                "traffic": 7365376, "traffic_algorithmic": 22691840}
 
     def cpu_sample(self):
         from oracle import linearq_oracle as O
