@@ -207,7 +207,10 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
     // so issuer w-1 takes the groups that land in buffer w-1: the two threads never touch the same
     // accumulator, each commit tracks only its own thread's MMAs, and shared-memory stages are
     // consumed independently, so they need no ordering between them.
-    if (lane == 0 && rank == 0) {
+    // The loop is run by the whole warp (counters, addresses and descriptors stay warp-uniform); only the
+    // tcgen05 instructions are under an elected lane.
+    if (rank == 0) {
+      const bool el = tc::elect_one();
       const uint32_t me = uint32_t(warp - 1);
       const uint32_t mrows = PAIR ? 256u : 128u;
       const uint32_t idesc = F8 ? tc::instr_desc(1u, 0u, mrows, uint32_t(p.bt)) : tc::instr_desc(2u, 1u, mrows, uint32_t(p.bt));
@@ -236,28 +239,30 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
             const uint32_t d_tmem = tmem_base + buf * uint32_t(p.bt);
             // a K step of 32 bytes = +2 in the descriptor's 16-byte address field
             const uint64_t da = tc::smem_desc_sw128(sb), db = tc::smem_desc_sw128(sb + kW8TileBytes);
-            if (PAIR) {
-              tc::mma_8bit_pair<F8>(d_tmem, da, db, idesc, uint32_t(gb != 0));
-              tc::mma_8bit_pair<F8>(d_tmem, da + 2, db + 2, idesc, 1u);
-              tc::mma_8bit_pair<F8>(d_tmem, da + 4, db + 4, idesc, 1u);
-              tc::mma_8bit_pair<F8>(d_tmem, da + 6, db + 6, idesc, 1u);
-            } else if (F8) {
-              tc::mma_f8(d_tmem, da, db, idesc, uint32_t(gb != 0));
-              tc::mma_f8(d_tmem, da + 2, db + 2, idesc, 1u);
-              tc::mma_f8(d_tmem, da + 4, db + 4, idesc, 1u);
-              tc::mma_f8(d_tmem, da + 6, db + 6, idesc, 1u);
-            } else {
-              tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
-              tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
-              tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
-              tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
-            }
-            if (PAIR) {
-              tc::mma_commit_pair(empty_bar(s), 3);
-              if (gb + 1 == p.blocks_per_group) tc::mma_commit_pair(accf_bar(buf), 3);
-            } else {
-              tc::mma_commit(empty_bar(s));
-              if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(buf));
+            if (el) {
+              if (PAIR) {
+                tc::mma_8bit_pair<F8>(d_tmem, da, db, idesc, uint32_t(gb != 0));
+                tc::mma_8bit_pair<F8>(d_tmem, da + 2, db + 2, idesc, 1u);
+                tc::mma_8bit_pair<F8>(d_tmem, da + 4, db + 4, idesc, 1u);
+                tc::mma_8bit_pair<F8>(d_tmem, da + 6, db + 6, idesc, 1u);
+              } else if (F8) {
+                tc::mma_f8(d_tmem, da, db, idesc, uint32_t(gb != 0));
+                tc::mma_f8(d_tmem, da + 2, db + 2, idesc, 1u);
+                tc::mma_f8(d_tmem, da + 4, db + 4, idesc, 1u);
+                tc::mma_f8(d_tmem, da + 6, db + 6, idesc, 1u);
+              } else {
+                tc::mma_i8(d_tmem, da, db, idesc, uint32_t(gb != 0));
+                tc::mma_i8(d_tmem, da + 2, db + 2, idesc, 1u);
+                tc::mma_i8(d_tmem, da + 4, db + 4, idesc, 1u);
+                tc::mma_i8(d_tmem, da + 6, db + 6, idesc, 1u);
+              }
+              if (PAIR) {
+                tc::mma_commit_pair(empty_bar(s), 3);
+                if (gb + 1 == p.blocks_per_group) tc::mma_commit_pair(accf_bar(buf), 3);
+              } else {
+                tc::mma_commit(empty_bar(s));
+                if (gb + 1 == p.blocks_per_group) tc::mma_commit(accf_bar(buf));
+              }
             }
           }
           if (++s == nst) { s = 0; ph ^= 1u; }
