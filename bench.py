@@ -183,11 +183,10 @@ class W4A4Config2(Workload):
     kernels = ["hadamard_quant", "w4a4_gemm"]
 
     def e2e_step(self, i):
+        import asrq_b200
         xh = self.x_host[i % len(self.x_host)]
-        xd = xh.to(self.dev, non_blocking=True)
-        y = self.layer(xd)
-        self.y_host.copy_(y, non_blocking=True)
-        return xh.numel() * 2, y.numel() * 2
+        asrq_b200.forward_host(self.layer, xh, self.y_host, chunks=E2E_CHUNKS)
+        return xh.numel() * 2, self.y_host.numel() * 2
 
     def roofline(self, kernel_ms, peaks, int8_tops):
         ach = self.units_per_step() / (kernel_ms["w4a4_gemm"] * 1e-3) / 1e12
@@ -275,11 +274,10 @@ class W4A16Config1(Workload):
     kernels = ["gemm_a16_tc"]
 
     def e2e_step(self, i):
+        import asrq_b200
         xh = self.x_host[0]
-        xd = xh.to(self.dev, non_blocking=True)
-        y = self.layer(xd)
-        self.y_host.copy_(y, non_blocking=True)
-        return xh.numel() * 2, y.numel() * 2
+        asrq_b200.forward_host(self.layer, xh, self.y_host, chunks=E2E_CHUNKS)
+        return xh.numel() * 2, self.y_host.numel() * 2
 
     def roofline(self, kernel_ms, peaks, int8_tops):
         ach = self.units_per_step() / (kernel_ms["gemm_a16_tc"] * 1e-3) / 1e12
@@ -460,6 +458,8 @@ class DecodeLargeLayer(Workload):
         return {"kernel": "gemv_a16 (rounds variant)", "bound": "hbm", "achieved": ach, "unit": "GB/s",
                 "peak": peaks["hbm_gbs"], "frac": ach / peaks["hbm_gbs"], "of": peaks["source"], "traffic": None}
 
+
+E2E_CHUNKS = int(os.environ.get("ASRQ_BENCH_E2E_CHUNKS", "4"))  # token chunks of the host-to-host call (1: no overlap)
 
 WORKLOADS = {"c1": W4A16Config1, "c2": W4A4Config2, "c3": DecodeSweepConfig3, "large": DecodeLargeLayer}
 
@@ -688,7 +688,8 @@ def main():
             scale = 1e12 if wl.unit in ("TOP/s", "TFLOP/s") else 1e9
             e2e = {"value": wl.units_per_step() * world / (e2e_ms * 1e-3) / scale, "unit": wl.unit,
                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                   "api": (f"asrq_b200.{type(wl.layer).__name__}.forward on a pinned host tensor, result copied to pinned host memory"
+                   "api": (f"asrq_b200.forward_host({type(wl.layer).__name__}, pinned host in, pinned host out, chunks={E2E_CHUNKS}): "
+                           "copies in and out overlapped with the kernels chunk by chunk"
                            if hasattr(wl, "layer") else "the C-ABI decode calls with pinned host activations in and pinned host outputs back")}
         _lib.call("asrq_check_status", wl.ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
         return wl, total_ms / steps, kernel_ms, clocks, e2e

@@ -68,3 +68,37 @@ def test_fused_qkv_matches_whisper_shapes_with_leading_dims():
     for o, p in zip(outs, parts):
         assert o.shape == (2, 3, d)
         assert_close_rows(o.reshape(6, d), _ref_layer(p, x.reshape(6, d).float()), what="qkv")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("chunks", [1, 4, 7])
+def test_forward_host_matches_one_call(chunks):
+    """Host-to-host pipelined call against copying in, one forward, copying out: same bits when the chunks
+    are served by the same kernel as the whole batch, within the accuracy bar otherwise."""
+    import asrq_b200
+    from oracle import linearq_oracle as O
+    case = O.make_c1(seed=3, m=1000, k=1280, n=1280)
+    lq = asrq_b200.LinearQ(1280, 1280, 4, 128, bias=True).to("cuda:0")
+    lq.load_quantized_params(case["scales"], case["zeros"], case["weight"])
+    lq.bias = case["bias"].to("cuda:0")
+    xh = case["x"].pin_memory()
+    ref = lq(xh.to("cuda:0")).cpu()
+    out = torch.empty(1000, 1280, dtype=torch.float16).pin_memory()
+    got = asrq_b200.forward_host(lq, xh, out, chunks=chunks)
+    torch.cuda.synchronize()
+    assert got is out
+    ref32 = O.linearq_forward_fp32(case["x"], case["weight"], case["scales"], case["zeros"], case["bias"], 4, 128)
+    assert_close_rows(out, ref32, what=f"forward_host chunks={chunks}")
+    if chunks == 1:
+        assert torch.equal(out, ref)
+    x2, w2 = torch.randn(900, 4096).half(), torch.randn(256, 4096) * 0.02
+    qq = asrq_b200.LinearQQ(4096, 256, 4, 4, 128, bias=False).to("cuda:0")
+    pw, sw = asrq_b200.pack_w4a4(w2, 128, True)
+    qq.load_quantized_params(sw, torch.zeros_like(sw), pw)
+    ref2 = qq(x2.to("cuda:0")).cpu()
+    got2 = asrq_b200.forward_host(qq, x2.pin_memory(), chunks=chunks)
+    torch.cuda.synchronize()
+    scale = ref2.float().abs().max(dim=-1, keepdim=True).values
+    assert float(((got2.float() - ref2.float()).abs() / scale).max()) < 2e-3
+    if chunks == 1:
+        assert torch.equal(got2, ref2)
