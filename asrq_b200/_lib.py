@@ -64,6 +64,8 @@ SIGNATURES = {
     "asrq_hadamard_quant_f8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
     "asrq_w4a4_gemm_f8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "asrq_set_option": (c_int, [c_char_p, c_int]),
+    "asrq_get_option": (c_int, [c_char_p, ctypes.POINTER(c_int)]),
     "asrq_check_status": (c_int, [c_void_p, c_void_p]),
     "asrq_device_info_query": (c_int, [c_int, ctypes.POINTER(DeviceInfo)]),
 }
@@ -100,6 +102,17 @@ def check(fn_name: str, code: int) -> None:
 
 def call(fn_name: str, *args) -> None:
     check(fn_name, getattr(load(), fn_name)(*args))
+
+
+def set_option(name: str, value: int) -> None:
+    """Sets a tuning / test switch of the library (see asrq_set_option in the header)."""
+    call("asrq_set_option", name.encode(), int(value))
+
+
+def get_option(name: str) -> int:
+    v = c_int(0)
+    call("asrq_get_option", name.encode(), ctypes.byref(v))
+    return v.value
 
 
 def workspace_bytes(kind: int, m: int, n: int, k: int) -> int:

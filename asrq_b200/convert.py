@@ -102,8 +102,6 @@ class FusedLinearQ(nn.Module):
         for p in parts:
             if (p.in_features, p.bits, p.group_size) != (p0.in_features, p0.bits, p0.group_size):
                 raise ValueError("FusedLinearQ: parts differ in in_features, bits or group_size")
-            if (p.bias is None) != (p0.bias is None):
-                raise ValueError("FusedLinearQ: either all parts have a bias or none")
         self.parts = nn.ModuleList(parts)
         self._fused: Optional[LinearQ] = None
         self._key = None
@@ -114,12 +112,19 @@ class FusedLinearQ(nn.Module):
         if self._fused is None or key != self._key:
             p0 = self.parts[0]
             n = sum(p.out_features for p in self.parts)
-            f = LinearQ(p0.in_features, n, p0.bits, p0.group_size, bias=p0.bias is not None)
+            any_bias = any(p.bias is not None for p in self.parts)
+            f = LinearQ(p0.in_features, n, p0.bits, p0.group_size, bias=any_bias)
             f.weight = torch.cat([p.weight for p in self.parts], dim=0).contiguous()
             f.scales = torch.cat([p.scales for p in self.parts], dim=0).contiguous()
             f.zeros = torch.cat([p.zeros for p in self.parts], dim=0).contiguous()
-            if p0.bias is not None:
-                f.bias = torch.cat([p.bias for p in self.parts], dim=0).contiguous()
+            if any_bias:
+                f.bias = torch.cat([p.bias if p.bias is not None else
+                                    torch.zeros(p.out_features, dtype=torch.float16, device=p.weight.device)
+                                    for p in self.parts], dim=0).contiguous()
+            if f.weight.is_cuda:
+                # The decode kernels fetch weights ahead of their stream dependency (programmatic dependent
+                # launch): the concatenated buffers must be complete before the first call is enqueued.
+                torch.cuda.current_stream(f.weight.device).synchronize()
             # not registered as a submodule: the fused copy must not show up in state_dict
             object.__setattr__(self, "_fused", f)
             self._key = key

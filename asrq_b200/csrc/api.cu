@@ -3,6 +3,8 @@
 // memory or synchronises (asrq_check_status excepted, which says so).
 #include <algorithm>
 #include <atomic>
+#include <cctype>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -60,6 +62,43 @@ int cuda_fail(cudaError_t e, const char* what) {
   last_error() = buf;
   return int(e) > 0 ? int(e) : 1;
 }
+
+// ---- options ------------------------------------------------------------------------------
+namespace {
+struct OptionDef {
+  const char* name;
+  int def;
+};
+const OptionDef kOptionDefs[kOptCount] = {
+    {"no_pdl", 0},      {"gemv_kernel", 0}, {"gemv_cpw", 0},  {"gemv_loop", -1},   {"tc_split", 0},   {"tc_bt", 0},
+    {"tc_pair", -1},    {"tc_pair_release", 0}, {"w4a4_bt", 0}, {"w4a4_pair", -1}, {"trace", 0},      {"trace_block", 0},
+};
+struct OptionTable {
+  std::atomic<int> v[kOptCount];
+  std::atomic<unsigned> generation{0};
+  OptionTable() {
+    for (int i = 0; i < kOptCount; ++i) {
+      std::string env = "ASRQ_B200_";
+      for (const char* c = kOptionDefs[i].name; *c; ++c) env.push_back(char(toupper(*c)));
+      const char* e = getenv(env.c_str());
+      v[i].store(e && *e ? atoi(e) : kOptionDefs[i].def);
+    }
+  }
+};
+OptionTable& option_table() {
+  static OptionTable t;  // environment read once, at first use
+  return t;
+}
+int find_option(const char* name) {
+  if (!name) return -1;
+  for (int i = 0; i < kOptCount; ++i)
+    if (!strcmp(name, kOptionDefs[i].name)) return i;
+  return -1;
+}
+}  // namespace
+
+int option(Option o) { return option_table().v[o].load(std::memory_order_relaxed); }
+unsigned options_generation() { return option_table().generation.load(std::memory_order_relaxed); }
 
 // ---- per-device facts ---------------------------------------------------------------------
 struct DeviceFacts {
@@ -317,7 +356,9 @@ int asrq_w4a4_gemm(const uint8_t* qa, const float* sa, const uint8_t* qw, const 
   if (!qa || !sa || !qw || !sw || !y) return fail(ASRQ_ERR_NULL, "asrq_w4a4_gemm: qa, sa, qw, sw and y must not be NULL");
   if (!workspace || workspace_bytes < kStatusBytes) return fail(ASRQ_ERR_WORKSPACE, "asrq_w4a4_gemm: workspace");
   if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_w4a4_gemm: dtype %d", dtype);
-  if (M < 0 || N <= 0 || K <= 0) return fail(ASRQ_ERR_SHAPE, "asrq_w4a4_gemm: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (M < 0 || N <= 0 || K <= 0 || group_size <= 0)
+    return fail(ASRQ_ERR_SHAPE, "asrq_w4a4_gemm: M=%lld N=%lld K=%lld group_size=%d", (long long)M, (long long)N,
+                (long long)K, group_size);
   if (!aligned16(qa) || !aligned16(qw) || !aligned16(y) || !aligned16(workspace))
     return fail(ASRQ_ERR_ALIGN, "asrq_w4a4_gemm: qa, qw, y and workspace must be 16-byte aligned");
   const DeviceFacts* f;
@@ -426,6 +467,23 @@ int asrq_w4a4_gemm_f8(const uint8_t* a8, const float* sa, const uint8_t* w8, con
                       void* workspace, size_t workspace_bytes, void* stream) {
   return gemm_operand("asrq_w4a4_gemm_f8", a8, sa, w8, sw, bias, y, acc_dump, M, N, K, group_size, dtype, 2,
                       workspace, workspace_bytes, stream);
+}
+
+int asrq_set_option(const char* name, int value) {
+  last_error().clear();
+  const int i = find_option(name);
+  if (i < 0) return fail(ASRQ_ERR_SHAPE, "asrq_set_option: unknown option '%s'", name ? name : "(null)");
+  option_table().v[i].store(value);
+  option_table().generation.fetch_add(1);
+  return ASRQ_OK;
+}
+
+int asrq_get_option(const char* name, int* value) {
+  last_error().clear();
+  const int i = find_option(name);
+  if (i < 0 || !value) return fail(ASRQ_ERR_SHAPE, "asrq_get_option: unknown option '%s' or NULL result", name ? name : "(null)");
+  *value = option_table().v[i].load();
+  return ASRQ_OK;
 }
 
 int asrq_check_status(void* workspace, void* stream) {

@@ -27,6 +27,28 @@ int cuda_fail(cudaError_t e, const char* what);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- host: tuning and test switches (asrq_set_option / asrq_get_option) ------------------
+// Process-wide integers.  Each takes its default from the environment variable ASRQ_B200_<NAME>
+// (upper case) read ONCE, when the library is loaded; afterwards only asrq_set_option changes it.
+// No launch path calls getenv.
+enum Option {
+  kOptNoPdl = 0,     // 1: launch without programmatic dependent launch
+  kOptGemvKernel,    // decode kernel: 0 auto, 1 strip-per-block (registers), 2 split-K (workspace), 3 staged (shared memory)
+  kOptGemvCpw,       // strip-per-block decode kernel: steps per warp (0 auto)
+  kOptGemvLoop,      // strip-per-block decode kernel, rounds variant: -1 auto, 0 never, 1 whenever a layer needs > 1 wave
+  kOptTcSplit,       // prefill kernel: 1 disables split K
+  kOptTcBt,          // prefill kernels: token-tile width (0 auto)
+  kOptTcPair,        // prefill: -1 auto, 0 one CTA per tile, 1 CTA pairs
+  kOptTcPairRelease, // CTA-pair prefill: 1 = release-ordered cross-CTA arrivals (one per dequant warp), 0 = relaxed
+  kOptW4a4Bt,        // W4A4 GEMM: token-tile width (0 auto)
+  kOptW4a4Pair,      // W4A4 GEMM: -1 auto, 0 one CTA per tile, 1 CTA pairs
+  kOptTrace,         // builds with -DASRQ_TRACE only: 1 records pipeline clock marks into the workspace
+  kOptTraceBlock,    // builds with -DASRQ_TRACE only: which block records
+  kOptCount
+};
+int option(Option o);
+unsigned options_generation();  // bumped by every asrq_set_option: caches of derived choices compare it
+
 // ---- workspace layout --------------------------------------------------------------
 // [0,256)            status block: word 0 = error flag (0 ok), word 1 = where a wait gave up
 // [256, 256+16384)   4096 tile counters (zero between calls)

@@ -37,7 +37,7 @@ struct GemmTcParams {
   const __half* bias;
   uint16_t* y;
   unsigned* status;
-  long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
+  long long* trace;  // builds with -DASRQ_TRACE: when not NULL, block 0 records clock64() at pipeline milestones
   float* partials;    // split-K: fp32 partial tiles [tile][split][bt tokens][128 features]
   unsigned* counters; // split-K: one arrival counter per (tile, lane quadrant), zero between launches
   int M, N, K, group_size, groups_per_row, bt, nstages, n_ftiles, n_ttiles;
@@ -141,10 +141,14 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
 
   const int nkb = p.K / 64;
   const int nitems = p.n_ftiles * p.n_ttiles * p.ksplit;
+#ifdef ASRQ_TRACE
   const bool tr = p.trace != nullptr && blockIdx.x == 0;
   auto mark = [&](int role, uint32_t i, int slot) {
     if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
   };
+#else
+  auto mark = [](int, uint32_t, int) {};  // the shipped kernels carry no trace branches
+#endif
 
   // Ring positions are carried as (index, phase) counters: the role loops below run on one
   // thread (or one warp per scheduler), where every integer division costs ~150 cycles of
@@ -425,10 +429,8 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
 // Token-tile width: the multiple of 32 (<= 256, <= M) that minimises
 // rounds-over-the-SMs x (tile width + fixed per-tile overhead).
 int gemm_tc_pick_bt(int64_t M, int64_t N, int sm_count) {
-  if (const char* e = getenv("ASRQ_B200_TC_BT")) {  // tuning knob: force the token-tile width
-    const int v = atoi(e);
-    if (v >= 32 && v <= 256 && v % 32 == 0) return v;
-  }
+  const int forced = option(kOptTcBt);  // tuning knob: force the token-tile width
+  if (forced >= 32 && forced <= 256 && forced % 32 == 0) return forced;
   int best = 32;
   double best_cost = 1e30;
   const int64_t nft = N / 128;
@@ -450,9 +452,7 @@ int gemm_tc_pick_bt(int64_t M, int64_t N, int sm_count) {
 // count, by two K blocks per part, and by the partial-sum area the workspace contract provides
 // (split x padded M <= 512, the skinny kernel's 2048 bytes per output feature).
 int gemm_tc_pick_split(int64_t M, int64_t N, int64_t K, int bt, int sm_count) {
-  if (const char* e = getenv("ASRQ_B200_TC_SPLIT")) {  // tuning knob: 1 disables
-    if (atoi(e) == 1) return 1;
-  }
+  if (option(kOptTcSplit) == 1) return 1;  // tuning knob: 1 disables
   const int64_t n_tt = (M + bt - 1) / bt, tiles = (N / 128) * n_tt, nkb = K / 64;
   int64_t split = std::min<int64_t>({int64_t(sm_count) / tiles, nkb / 2, 512 / (n_tt * bt), kTcMaxSplit});
   return int(std::max<int64_t>(split, 1));
@@ -475,7 +475,7 @@ static int launch_tc(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmT
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = getenv("ASRQ_B200_NO_PDL") ? 0 : 1;
+  cfg.numAttrs = option(kOptNoPdl) ? 0 : 1;
   ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmx, tmw, p));
   return ASRQ_OK;
 }
@@ -490,9 +490,9 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
   // The CTA-pair kernel (gemm_a16_tc2.cu, tcgen05 cta_group::2: half the activation rows per SM per
   // MMA) takes large M where the shape allows (20.9 us against 23.1 us on M=1500 K=1280 N=5120); M <= 256
-  // stays here for the K split.  ASRQ_B200_TC_PAIR=1 / 0 forces / forbids it.
-  const char* pair_env = getenv("ASRQ_B200_TC_PAIR");
-  const bool want_pair = pair_env ? atoi(pair_env) != 0 : M > 256;
+  // stays here for the K split.  Option "tc_pair" = 1 / 0 forces / forbids it.
+  const int pair_opt = option(kOptTcPair);
+  const bool want_pair = pair_opt >= 0 ? pair_opt != 0 : M > 256;
   if (want_pair && gemm_a16_tc2_supports(M, N, K, group_size))
     return gemm_a16_tc2(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
                         sm_count, stream);
@@ -512,9 +512,11 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
   // diagnostic timeline (4 roles x 512 events x 2 clocks), only on request and only if the workspace has room
-  p.trace = (getenv("ASRQ_B200_TRACE") && workspace_bytes >= (1u << 20) + 4 * 512 * 2 * 8)
-                ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20))
-                : nullptr;
+  p.trace = nullptr;
+#ifdef ASRQ_TRACE
+  if (option(kOptTrace) && workspace_bytes >= (1u << 20) + 4 * 512 * 2 * 8)
+    p.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20));
+#endif
   p.M = int(M);
   p.N = int(N);
   p.K = int(K);

@@ -36,6 +36,7 @@ struct GemmTc2Params {
   uint16_t* y;
   unsigned* status;
   int M, N, K, group_size, groups_per_row, bt, nstages, n_fpairs, n_ttiles;
+  int release_arrive;  // 1: the peer CTA's "A slot written" arrivals carry release semantics at cluster scope
 };
 
 constexpr int kT2Groups = 3;
@@ -80,13 +81,21 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + b); };
   auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 2 + b); };
   // One arrival per warp on a barrier of CTA 0, from either CTA, after every lane has made its writes
-  // visible to the async proxy.  The remote arrival is relaxed: with release semantics at cluster
-  // scope it stalls the arriving warp for ~1000 cycles.
-  auto arrive_on_leader = [&](uint32_t bar) {
+  // visible to the async proxy (fence.proxy.async) and the warp has synchronised.
+  // "Accumulator drained" carries no data through memory (the values are in registers), so its remote
+  // arrival is relaxed.  "A slot written" hands over shared-memory contents of the peer CTA that the
+  // pair's MMA then reads: `release` selects mbarrier.arrive.release.cluster for it (the memory model's
+  // release/acquire edge; it stalls the arriving warp ~1000 cycles).  The relaxed form relies on the
+  // hardware performing a CTA's own shared-memory stores, and the proxy fence after them, before a later
+  // remote arrival of the same thread leaves the SM; tests/test_gpu_a16.py repeats large shapes and
+  // compares both forms bit for bit with the one-CTA kernel.
+  auto arrive_on_leader = [&](uint32_t bar, bool release) {
     __syncwarp();
     if (lane == 0) {
       if (rank == 0) {
         tc::mbar_arrive(bar);
+      } else if (release) {
+        tc::mbar_arrive_cluster(tc::mapa(bar, 0));
       } else {
         tc::mbar_arrive_cluster_relaxed(tc::mapa(bar, 0));
       }
@@ -162,7 +171,9 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         // the accumulator buffer must have been drained by both CTAs
         ok = tc::mbar_wait_spin(acce_bar(buf), ((ucount >> 1) & 1u) ^ 1u, p.status, 2);
         for (int kb = 0; kb < nkb && ok; ++kb) {
-          ok = tc::mbar_wait_spin(deq_bar(a), dph, p.status, 4) && tc::mbar_wait_spin(full_bar(s), ph, p.status, 3);
+          ok = (p.release_arrive ? tc::mbar_wait_spin_cluster(deq_bar(a), dph, p.status, 4)
+                                 : tc::mbar_wait_spin(deq_bar(a), dph, p.status, 4)) &&
+               tc::mbar_wait_spin(full_bar(s), ph, p.status, 3);
           if (!ok) break;
           tc::fence_after_sync();
           // a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address field
@@ -239,7 +250,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         }
       }
       tc::fence_proxy_async_smem();
-      arrive_on_leader(deq_bar(a));
+      arrive_on_leader(deq_bar(a), p.release_arrive != 0);
       unit = nunit;
       kb = nk;
       s += kT2Groups;
@@ -282,7 +293,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         }
       }
       tc::fence_before_sync();
-      arrive_on_leader(acce_bar(buf));
+      arrive_on_leader(acce_bar(buf), false);
     }
   }
 
@@ -299,10 +310,8 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
 // Token-tile width: the multiple of 32 (<= 256, <= M) that minimises rounds over the CTA pairs x
 // (tile width + fixed per-tile overhead).
 int pick_bt(int64_t M, int64_t npairs, int nclusters) {
-  if (const char* e = getenv("ASRQ_B200_TC_BT")) {  // tuning knob: force the token-tile width
-    const int v = atoi(e);
-    if (v >= 32 && v <= 256 && v % 32 == 0) return v;
-  }
+  const int forced = option(kOptTcBt);  // tuning knob: force the token-tile width
+  if (forced >= 32 && forced <= 256 && forced % 32 == 0) return forced;
   int best = 32;
   double best_cost = 1e30;
   for (int bt = 32; bt <= 256; bt += 32) {
@@ -357,6 +366,7 @@ int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, 
   p.group_size = group_size;
   p.groups_per_row = int(K / group_size);
   p.n_fpairs = int(N / 256);
+  p.release_arrive = option(kOptTcPairRelease);
   const int max_clusters = sm_count / 2;
   p.bt = pick_bt(M, p.n_fpairs, max_clusters);
   p.n_ttiles = int((M + p.bt - 1) / p.bt);

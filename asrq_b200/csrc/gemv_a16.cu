@@ -42,7 +42,7 @@ struct GemvParams {
   uint16_t* y;
   int M, N, K, groups_per_row, KQ, CPW, bf16;  // CPW repeats the kernel's template argument
   int R;                                       // rounds (LOOP variants): a warp takes R runs of CPW steps, KQ * CPW steps apart
-  unsigned long long* trace;  // diagnostic: per-warp clock marks (8 words per warp), NULL normally
+  unsigned long long* trace;  // builds with -DASRQ_TRACE: per-warp clock marks (8 words per warp), NULL otherwise
 };
 
 constexpr int kGemvMaxWarps = 16;
@@ -378,9 +378,15 @@ using GemvKernel = void (*)(const GemvParams);
 
 template <int BITS, int MH, int GPS, int CPW>
 GemvKernel kernel_for(bool xc, bool trace) {
-  if (MH == 1 && xc)
-    return trace ? gemv_a16_kernel<BITS, 1, GPS, CPW, true, true> : gemv_a16_kernel<BITS, 1, GPS, CPW, true, false>;
-  return trace ? gemv_a16_kernel<BITS, MH, GPS, CPW, false, true> : gemv_a16_kernel<BITS, MH, GPS, CPW, false, false>;
+#ifdef ASRQ_TRACE
+  if (trace) {
+    if (MH == 1 && xc) return gemv_a16_kernel<BITS, 1, GPS, CPW, true, true>;
+    return gemv_a16_kernel<BITS, MH, GPS, CPW, false, true>;
+  }
+#endif
+  (void)trace;  // the shipped library holds no trace variants
+  if (MH == 1 && xc) return gemv_a16_kernel<BITS, 1, GPS, CPW, true, false>;
+  return gemv_a16_kernel<BITS, MH, GPS, CPW, false, false>;
 }
 template <int BITS, int MH>
 GemvKernel kernel_for(int gps, int cpw, bool xc, bool trace) {
@@ -438,7 +444,7 @@ struct GemvSplit {
 GemvSplit gemv_pick_split(int bits, int mh, int gps, bool xc, bool trace, int64_t N, int64_t K, int sm_count) {
   const int stepk = bits == 4 ? 128 : 256;
   const int steps = int(K / stepk);
-  static const int cpw_env = getenv("ASRQ_B200_GEMV_CPW") ? atoi(getenv("ASRQ_B200_GEMV_CPW")) : 0;  // tuning knob
+  const int cpw_env = option(kOptGemvCpw);  // tuning knob
   GemvSplit best;
   best.KQ = best.CPW = 0;
   best.kern = nullptr;
@@ -469,7 +475,7 @@ GemvSplit gemv_pick_split(int bits, int mh, int gps, bool xc, bool trace, int64_
   }
   // Layers that do not fit one resident wave (or whose K is longer than 16 warps x 4 steps): small
   // blocks that walk K in rounds, so that the blocks sharing an SM overlap loads and arithmetic.
-  static const int loop_env = getenv("ASRQ_B200_GEMV_LOOP") ? atoi(getenv("ASRQ_B200_GEMV_LOOP")) : -1;  // tuning knob
+  const int loop_env = option(kOptGemvLoop);  // tuning knob
   const bool large = N * K * bits / 8 >= (int64_t(16) << 20);
   if (!trace && loop_env != 0 && (!best.kern || (best_waves > 1 && (large || loop_env == 1)))) {
     int cpw = 0;
@@ -496,6 +502,14 @@ GemvSplit cached_split(int bits, int cls, int gps, bool trace, int64_t N, int64_
   };
   static std::mutex mu;
   static std::vector<Entry> cache;
+  static unsigned cache_generation = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache_generation != options_generation()) {  // a tuning option changed: choose again
+      cache.clear();
+      cache_generation = options_generation();
+    }
+  }
   const uint64_t key = (uint64_t(N) << 40) ^ (uint64_t(K) << 16) ^ (uint64_t(sm_count) << 6) ^ (uint64_t(gps) << 3) ^
                        (uint64_t(cls) << 1) ^ uint64_t(bits == 4);
   {
@@ -520,7 +534,7 @@ int launch_gemv(const GemvSplit& sp, const GemvParams& p, cudaStream_t stream) {
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  static const bool pdl = getenv("ASRQ_B200_NO_PDL") == nullptr;
+  const bool pdl = option(kOptNoPdl) == 0;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, sp.kern, p));
@@ -544,8 +558,12 @@ int gemv_a16(int bits, const void* x, const uint8_t* w, const void* scales, cons
     return fail(ASRQ_ERR_WORKSPACE, "w%da16 gemv: workspace %zu < %zu bytes", bits, workspace_bytes,
                 gemv_workspace_bytes(N, max_split));
   const int gps = chunk % group_size == 0 ? chunk / group_size : 0;  // groups per step: 1, 2 or 4
-  static const bool force_splitk = getenv("ASRQ_B200_GEMV_SPLITK") != nullptr;
-  static const bool trace = getenv("ASRQ_B200_TRACE") != nullptr;
+  const bool force_splitk = option(kOptGemvKernel) == 2;
+#ifdef ASRQ_TRACE
+  const bool trace = option(kOptTrace) != 0;
+#else
+  const bool trace = false;
+#endif
   if (force_splitk || (gps != 1 && gps != 2 && gps != 4) || !aligned16(scales) || !aligned16(zeros))
     return gemv_a16_splitk(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace,
                            workspace_bytes, sm_count, stream, max_split);

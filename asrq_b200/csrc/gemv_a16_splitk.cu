@@ -325,7 +325,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  static const bool pdl = getenv("ASRQ_B200_NO_PDL") == nullptr;
+  const bool pdl = option(kOptNoPdl) == 0;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));

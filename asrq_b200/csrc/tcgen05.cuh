@@ -76,6 +76,32 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, un
   }
 }
 
+// Acquire at cluster scope: pairs with mbarrier.arrive.release.cluster from the other CTA of a pair.
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin_cluster(uint32_t bar, uint32_t parity, unsigned* status, unsigned site) {
+  if (mbar_test_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_test_wait_cluster(bar, parity)) return true;
+    if (clock64() - t0 > kWaitCycles) {
+      if (atomicCAS(status, 0u, 1u) == 0u) status[1] = site;
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned site) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();

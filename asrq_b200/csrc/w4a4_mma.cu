@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(128) w4a4_mma_kernel(const W4A4Params p) {
 int w4a4_gemm_mma(const uint8_t* qa, const float* sa, const uint8_t* qw, const void* sw, const void* bias,
                   void* y, int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
                   cudaStream_t stream) {
-  if (N % 64 || K % 128 || group_size % 128 || K % group_size)
+  if (group_size <= 0 || N % 64 || K % 128 || group_size % 128 || K % group_size)
     return fail(ASRQ_ERR_SHAPE,
                 "w4a4 gemm: need N%%64==0, K%%128==0, group_size%%128==0, K%%group_size==0 "
                 "(N=%lld K=%lld g=%d)", (long long)N, (long long)K, group_size);

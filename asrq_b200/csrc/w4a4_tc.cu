@@ -86,7 +86,7 @@ struct W4A4TcParams {
   uint16_t* y;
   int32_t* acc_dump;
   unsigned* status;
-  long long* trace;  // diagnostic: when not NULL, block 0 records clock64() at pipeline milestones
+  long long* trace;  // builds with -DASRQ_TRACE: when not NULL, block `trace_block` records clock64() at pipeline milestones
   int M, N, K, groups, blocks_per_group, bt, nbuf, nstages, n_ftiles, n_ttiles, bf16, trace_block;
 };
 
@@ -172,10 +172,14 @@ __device__ __forceinline__ void w4a4_tc_body(const CUtensorMap* tmw_p, const CUt
   const int n_ft = PAIR ? p.n_ftiles / 2 : p.n_ftiles;
   const int ntiles = n_ft * p.n_ttiles;
   const int nkb = p.K / 128;
+#ifdef ASRQ_TRACE
   const bool tr = p.trace != nullptr && int(blockIdx.x) == p.trace_block;
   auto mark = [&](int role, uint32_t i, int slot) {
     if (tr && i < 512) p.trace[(role * 512 + i) * 2 + slot] = clock64();
   };
+#else
+  auto mark = [](int, uint32_t, int) {};  // the shipped kernels carry no trace branches
+#endif
 
   // Ring positions are (index, phase) counters: no integer division inside the role loops.
   if (warp == 0) {
@@ -406,7 +410,7 @@ struct W4A4Tile {
 };
 // `N` and `sm_count` are halved by the caller for the CTA-pair kernel (feature-tile pairs over CTA pairs).
 static W4A4Tile w4a4_pick_tile(int64_t M, int64_t N, int sm_count) {
-  static const int bt_env = getenv("ASRQ_B200_W4A4_BT") ? atoi(getenv("ASRQ_B200_W4A4_BT")) : 0;  // tuning knob
+  const int bt_env = option(kOptW4a4Bt);  // tuning knob
   if (bt_env > 0 && bt_env <= 192 && (bt_env % 48 == 0 || bt_env % 64 == 0))
     return {bt_env, bt_env % 48 == 0 ? 3 : 4};
   W4A4Tile best = {48, 3};
@@ -457,19 +461,21 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   p.acc_dump = acc_dump;
   p.status = static_cast<unsigned*>(workspace);
   // diagnostic timeline (3 roles x 512 events x 2 clocks), only on request and only if the workspace has room
-  p.trace = (getenv("ASRQ_B200_TRACE") && workspace_bytes >= (1u << 20) + 3 * 512 * 2 * 8)
-                ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20))
-                : nullptr;
-  p.trace_block = getenv("ASRQ_B200_TRACE_BLOCK") ? atoi(getenv("ASRQ_B200_TRACE_BLOCK")) : 0;
+  p.trace = nullptr;
+  p.trace_block = 0;
+#ifdef ASRQ_TRACE
+  if (option(kOptTrace) && workspace_bytes >= (1u << 20) + 3 * 512 * 2 * 8)
+    p.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + (1u << 20));
+  p.trace_block = option(kOptTraceBlock);
+#endif
   p.M = int(M);
   p.N = int(N);
   p.K = int(K);
   p.groups = int(K / group_size);
   p.blocks_per_group = group_size / 128;
   // CTA pairs (tcgen05 cta_group::2) halve the activation bytes an SM takes in per MMA; they need an even
-  // number of feature tiles.  ASRQ_B200_W4A4_PAIR=0 / 1 forces the choice (tuning knob).
-  const char* pair_str = getenv("ASRQ_B200_W4A4_PAIR");
-  const int pair_env = pair_str ? atoi(pair_str) : -1;
+  // number of feature tiles.  Option "w4a4_pair" = 0 / 1 forces the choice (tuning knob).
+  const int pair_env = option(kOptW4a4Pair);
   const bool pair = (N / 128) % 2 == 0 && sm_count >= 2 && pair_env != 0 && (pair_env == 1 || kW4A4PairDefault);
   const W4A4Tile tile = pair ? w4a4_pick_tile(M, N / 2, sm_count / 2) : w4a4_pick_tile(M, N, sm_count);
   p.bt = tile.bt;
@@ -513,7 +519,7 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = getenv("ASRQ_B200_NO_PDL") ? 0 : 1;
+  cfg.numAttrs = option(kOptNoPdl) ? 0 : 1;
   ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmw, tma, p));
   return ASRQ_OK;
 }

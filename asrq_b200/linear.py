@@ -37,7 +37,29 @@ def check_status(device=None) -> None:
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is not None:
-        _lib.call("asrq_check_status", ws.data_ptr(), key[1])
+        with _on_device(device):
+            _lib.call("asrq_check_status", ws.data_ptr(), key[1])
+
+
+class _on_device:
+    """Makes the tensor's device current around C-ABI calls (the library works on the current device:
+    per-device facts, occupancy queries, launches).  Free when it already is."""
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _as_2d(x: torch.Tensor, k: int) -> torch.Tensor:
@@ -119,6 +141,8 @@ class LinearQ(nn.Module):
             raise TypeError("LinearQ.bias must be float16 on the input's device")
 
     def forward(self, input):
+        # fp16 / bf16 only (the reference computes in whatever dtype the input has, asrq/core/linear.py:58-59;
+        # an fp32 input raises here rather than silently running a slower path)
         dt = _require_cuda_16bit(input, "LinearQ.forward")
         if self.bits not in (2, 4):
             raise NotImplementedError("LinearQ.forward: bits must be 2 or 4")
@@ -131,9 +155,10 @@ class LinearQ(nn.Module):
             return y.reshape(*input.shape[:-1], n)
         ws = _workspace(input.device, _lib.workspace_bytes(_lib.WS_LINEARQ, m, n, k))
         stream = torch.cuda.current_stream(input.device).cuda_stream
-        _lib.call("asrq_linearq_a16", self.bits, x2.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
-                  self.zeros.data_ptr(), None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
-                  m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
+        with _on_device(input.device):
+            _lib.call("asrq_linearq_a16", self.bits, x2.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
+                      self.zeros.data_ptr(), None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
+                      m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
         if _CHECK:
             check_status(input.device)
         return y.reshape(*input.shape[:-1], n)
@@ -181,7 +206,9 @@ class LinearQQ(LinearQ):
     def quantize_activation(self, input):
         """(codes, scales): integer-valued float codes (M,K) and per-token scales (M,1), the
         return convention of the reference method (linear.py:77-82), computed by the CUDA prologue."""
-        qa, sa, _, _ = self._quantize(input)
+        _require_cuda_16bit(input, "LinearQQ")
+        with _on_device(input.device):
+            qa, sa, _, _ = self._quantize(input)
         p = qa.to(torch.int32)
         lo, hi = p & 0xF, (p >> 4) & 0xF
         lo = torch.where(lo >= 8, lo - 16, lo)
@@ -217,6 +244,11 @@ class LinearQQ(LinearQ):
         return m >= 64 and n % 128 == 0 and k % 128 == 0 and g % 128 == 0 and k % g == 0
 
     def forward(self, input, acc_dump=None, two_call=False):
+        _require_cuda_16bit(input, "LinearQQ")
+        with _on_device(input.device):
+            return self._forward(input, acc_dump, two_call)
+
+    def _forward(self, input, acc_dump=None, two_call=False):
         """``two_call=True`` forces the packed-activation sequence (asrq_hadamard_quant_int4 then
         asrq_w4a4_gemm); the default for large M is the prologue writing 8-bit operands directly.
         Both produce the same bits."""

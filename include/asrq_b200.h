@@ -15,6 +15,14 @@
  *   - the caller owns all memory, including the scratch `workspace`
  *     (size from asrq_workspace_bytes); no entry point allocates, frees or
  *     synchronises, so all of them are safe on any stream;
+ *   - the buffers' device must be the CURRENT device of the calling thread (the library reads
+ *     cudaGetDevice for its per-device facts and launches there);
+ *   - constant operands (packed weights, scales, zeros, bias) must be complete in memory before
+ *     the call is ENQUEUED, not merely ordered before it on the stream: the decode kernels are
+ *     launched with programmatic dependent launch and fetch these operands before they wait for
+ *     the preceding kernel on the stream.  After writing or repacking weights on a stream,
+ *     synchronise that stream once (or set option "no_pdl") before the first call that uses them.
+ *     Activations, outputs and the workspace carry ordinary stream ordering;
  *   - all matrices are row-major and contiguous.  `dtype` selects the 16-bit
  *     activation / output format (ASRQ_F16 or ASRQ_BF16); scales, zeros and bias
  *     are always fp16, as LinearQ registers them (linear.py:18-25).
@@ -207,6 +215,25 @@ int asrq_w4a4_gemm_f8(const uint8_t* a8, const float* sa, const uint8_t* w8, con
                       const void* bias, void* y, int32_t* acc_dump, int64_t M, int64_t N,
                       int64_t K, int group_size, int dtype, void* workspace,
                       size_t workspace_bytes, void* stream);
+
+/*
+ * Tuning and test switches, process-wide integers.  Each option takes its default from the
+ * environment variable ASRQ_B200_<NAME IN UPPER CASE>, read once when the library is first used;
+ * afterwards only asrq_set_option changes it (no call path reads the environment).  Options:
+ *   no_pdl (0)            1: launch every kernel without programmatic dependent launch
+ *   gemv_kernel (0)       decode kernel: 0 auto, 1 strip per block, 2 split K through the workspace,
+ *                         3 weights staged in shared memory ahead of the stream dependency
+ *   gemv_cpw (0), gemv_loop (-1)   strip-per-block decode kernel: steps per warp, rounds variant
+ *   tc_split (0)          1: no split K in the prefill kernel
+ *   tc_bt (0), w4a4_bt (0)         token-tile width of the tcgen05 kernels (0 auto)
+ *   tc_pair (-1), w4a4_pair (-1)   CTA-pair variants: -1 auto, 0 off, 1 on
+ *   tc_pair_release (0)   CTA-pair prefill kernel: 1 = release/acquire at cluster scope on the
+ *                         cross-CTA "operand written" hand-off (slower), 0 = relaxed arrival
+ *   trace (0), trace_block (0)     only in builds with -DASRQ_TRACE: pipeline clock marks
+ * Returns ASRQ_ERR_SHAPE for an unknown name.  No counterpart in the reference.
+ */
+int asrq_set_option(const char* name, int value);
+int asrq_get_option(const char* name, int* value);
 
 /*
  * Reads the workspace status block back (this one DOES synchronise the stream).

@@ -13,6 +13,12 @@ reference code produced for them:
 * ``linearq_*.npz``  LinearQ.dequantize_weight / forward (asrq/core/linear.py:33-66) in
                      fp32 and fp16, on packed weights built from the reference RTN output.
 * ``hadamard_*.npz`` matmul_hadU (asrq/transforms/rotation/hadamard_utils.py:60-81).
+* ``w4a4_composite_*.npz`` the reference's own functions composed into the W4A4 layer the reference
+                     never assembles: matmul_hadU (fp32) on the activations and on the weight rows,
+                     RTNQuantizer (symmetric int4, g128) on the rotated weight, then
+                     activation_quantization_forward_patch around F.linear on the fake-quantised weight.
+                     A float result; the integer composite of this repository must agree with it to
+                     within float summation error (tests/test_oracle_golden.py states the bound).
 * ``actquant_*.npz`` activation_quantization_forward_patch (asrq/quantizers/activation.py:10-33)
                      with an identity weight, i.e. round(x/s)*s; and LinearQQ.quantize_activation
                      (asrq/core/linear.py:77-82).
@@ -157,6 +163,37 @@ def main(root):
     np.savez(os.path.join(HERE, "actquant_4bit.npz"),
              x=x.numpy(), fake_quant=y.numpy(),
              x2=x2.numpy(), q2=q2.numpy(), s2=s2.numpy())
+    # --- W4A4 composite out of the reference's own pieces --------------------
+    for (m, k, n, g) in ((24, 1024, 128, 128), (9, 4096, 64, 128)):
+        gen = torch.Generator().manual_seed(400 + k)
+        # heavy-tailed activations with outlier channels, like the W4A4 benchmark configuration
+        z = torch.randn(m, k, generator=gen)
+        c = torch.zeros(m, k)
+        for _ in range(4):
+            c += torch.randn(m, k, generator=gen) ** 2
+        x = z / torch.sqrt(c / 4)
+        x[:, torch.randperm(k, generator=gen)[:8]] *= 20
+        x = x.half()
+        w = torch.randn(n, k, generator=gen) * 0.02
+        bias = (torch.randn(n, generator=gen) * 0.02).half()
+        lin = torch.nn.Linear(k, n, bias=True)
+        lin.weight.data = hu.matmul_hadU(w.clone())           # offline fold of the rotation into the weight
+        lin.bias.data = bias.float()
+        qz = RTNQuantizer(lin, "l", Cfg(4, g, True))          # fake-quantises lin.weight in place
+        scales, _ = qz()
+        act_patch(lin, 4, "l")                                # forward = fake act-quant + F.linear
+        with torch.no_grad():
+            v = hu.matmul_hadU(x.float())                     # online rotation, fp32
+            y = lin(v)
+        # the reference's fake-quantised weight, stored as the integer codes it implies (codes * scales
+        # reproduces it bit for bit, checked here) to keep the fixture small
+        fq = lin.weight.data.reshape(n, k // g, g)
+        w_codes = torch.round(fq / scales)
+        assert torch.equal(w_codes * scales, fq) and float(w_codes.abs().max()) <= 7
+        np.savez_compressed(os.path.join(HERE, f"w4a4_composite_k{k}.npz"),
+                            x=x.numpy().view(np.uint16), w=w.numpy(), bias=bias.numpy().view(np.uint16), group_size=g,
+                            w_codes=w_codes.reshape(n, k).to(torch.int8).numpy(), w_scales=scales.squeeze(-1).numpy(),
+                            v=v.numpy(), y=y.numpy())
     print("fixtures written to", HERE)
 
 

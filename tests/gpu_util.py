@@ -9,6 +9,50 @@ from oracle import linearq_oracle as O
 DEV = "cuda:0"
 
 
+class lib_option:
+    """``with lib_option("tc_pair", 1): ...`` sets a switch of the library (asrq_set_option) and puts
+    the previous value back afterwards."""
+
+    def __init__(self, name, value):
+        self.name, self.value = name, value
+
+    def __enter__(self):
+        self.old = _lib.get_option(self.name)
+        _lib.set_option(self.name, self.value)
+        return self
+
+    def __exit__(self, *exc):
+        _lib.set_option(self.name, self.old)
+        return False
+
+
+CANARY = 0xA5
+
+
+def padded(shape, dtype, device=DEV, pad_bytes=4096, fill=None):
+    """A tensor of ``shape`` carved out of a larger allocation whose leading and trailing ``pad_bytes``
+    hold a canary pattern; :func:`check_canary` verifies that a kernel wrote neither (the stand-in
+    for a memory checker on machines where none may run)."""
+    n = 1
+    for s in shape:
+        n *= s
+    nbytes = n * torch.empty(0, dtype=dtype).element_size()
+    raw = torch.full((pad_bytes + nbytes + pad_bytes,), CANARY, dtype=torch.uint8, device=device)
+    t = raw[pad_bytes:pad_bytes + nbytes].view(dtype).reshape(shape)
+    if fill is not None:
+        t.fill_(fill)
+    t._canary_raw = raw  # keeps the allocation alive and findable
+    t._canary_pad = pad_bytes
+    return t
+
+
+def check_canary(t, what=""):
+    raw, pad = t._canary_raw, t._canary_pad
+    head, tail = raw[:pad], raw[raw.numel() - pad:]
+    assert bool((head == CANARY).all()), f"{what}: bytes BEFORE the buffer were overwritten"
+    assert bool((tail == CANARY).all()), f"{what}: bytes AFTER the buffer were overwritten"
+
+
 def f16(a):
     return torch.from_numpy(a.view(np.float16).copy())
 
@@ -52,10 +96,16 @@ def run_a16_abi(fn, case, dtype=torch.float16, device=DEV):
     w = case["weight"].to(device)
     s, z = case["scales"].to(device), case["zeros"].to(device)
     b = None if case["bias"] is None else case["bias"].to(device)
-    y = torch.empty(m, n, dtype=dtype, device=device)
-    ws = torch.zeros(max(_lib.workspace_bytes(_lib.WS_LINEARQ, m, n, k), 1 << 20), dtype=torch.uint8, device=device)
+    # output and workspace sit between canary bytes: a kernel that writes outside either fails the test
+    y = padded((m, n), dtype, device)
+    kind = _lib.WS_A16_GEMM if fn.endswith("gemm") else _lib.WS_LINEARQ
+    ws = padded((max(_lib.workspace_bytes(kind, m, n, k), _lib.workspace_bytes(_lib.WS_LINEARQ, m, n, k)),),
+                torch.uint8, device, fill=0)
     _lib.call(fn, x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr(), None if b is None else b.data_ptr(),
               y.data_ptr(), m, n, k, case["group_size"], _lib.F16 if dtype == torch.float16 else _lib.BF16,
               ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
     _lib.call("asrq_check_status", ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    check_canary(y, f"{fn} output")
+    check_canary(ws, f"{fn} workspace")
+    assert int(ws[:16640].view(torch.int32).abs().sum()) == 0, f"{fn}: status block or tile counters not clean"
     return y

@@ -95,3 +95,24 @@ def test_no_cpu_fallback():
     q = asrq_b200.LinearQQ(256, 128, 4, 4)
     with pytest.raises(RuntimeError, match="no CPU path"):
         q(torch.zeros(2, 256, dtype=torch.float16))
+
+
+def test_w4a4_gemm_rejects_nonpositive_group_size_on_the_host():
+    """group_size 0 used to reach a modulus (division by zero killed the process); it is an argument
+    error like any other, found before a device is touched."""
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096 + 16)
+    p = (ctypes.addressof(buf) + 15) & ~15
+    for gs in (0, -128):
+        rc = lib.asrq_w4a4_gemm(p, p, p, p, None, p, None, 8, 64, 128, gs, 0, p, 4096, None)
+        assert rc == -2 and "group_size" in _lib.last_error()
+
+
+def test_options_are_set_and_read_back():
+    assert _lib.get_option("tc_pair") == -1
+    _lib.set_option("tc_pair", 1)
+    assert _lib.get_option("tc_pair") == 1
+    _lib.set_option("tc_pair", -1)
+    with pytest.raises(_lib.AsrqError) as e:
+        _lib.set_option("no_such_switch", 1)
+    assert e.value.code == -2

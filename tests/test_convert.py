@@ -66,12 +66,10 @@ def test_fused_parts_keep_their_state_dict_entries():
     torch.manual_seed(2)
     m = Block()
     C.convert(m, bits=4, group_size=128, skip=("proj_out",))
-    # k_proj has no bias: fusing it with q and v must be refused, q with v is fine
-    try:
-        C.FusedLinearQ([m.q_proj, m.k_proj, m.v_proj])
-        raise AssertionError("mixed bias accepted")
-    except ValueError:
-        pass
+    # k_proj has no bias (as in Whisper's attention): its rows of the fused bias are zeros
+    qkv = C.FusedLinearQ([m.q_proj, m.k_proj, m.v_proj])._fuse()
+    assert qkv.out_features == 768 and torch.equal(qkv.bias[:256], m.q_proj.bias)
+    assert int(qkv.bias[256:512].abs().sum()) == 0 and torch.equal(qkv.bias[512:], m.v_proj.bias)
     f = C.FusedLinearQ([m.q_proj, m.v_proj])
     keys = set(f.state_dict())
     assert keys == {f"parts.{i}.{b}" for i in (0, 1) for b in ("weight", "scales", "zeros", "bias")}

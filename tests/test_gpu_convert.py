@@ -70,6 +70,21 @@ def test_fused_qkv_matches_whisper_shapes_with_leading_dims():
         assert_close_rows(o.reshape(6, d), _ref_layer(p, x.reshape(6, d).float()), what="qkv")
 
 
+def test_fused_qkv_with_mixed_bias():
+    """Whisper's attention: q and v have a bias, k has none (asrq/models/transformers/whisper.py:94-97)."""
+    torch.manual_seed(6)
+    d = 1280
+    q, k, v = nn.Linear(d, d), nn.Linear(d, d, bias=False), nn.Linear(d, d)
+    parts = [C.linearq_from_linear(l, 4, 128).to(DEV) for l in (q, k, v)]
+    assert parts[1].bias is None
+    fused = C.FusedLinearQ(parts)
+    for m in (1, 32, 200):
+        x = torch.randn(m, d).half()
+        outs = fused(x.to(DEV))
+        for o, p in zip(outs, parts):
+            assert_close_rows(o, _ref_layer(p, x.float()), what=f"mixed-bias qkv m={m}")
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("chunks", [1, 4, 7])
 def test_forward_host_matches_one_call(chunks):

@@ -12,7 +12,7 @@ import torch
 import asrq_b200
 from asrq_b200 import _lib
 from oracle import linearq_oracle as O
-from tests.gpu_util import DEV, assert_close_rows
+from tests.gpu_util import DEV, assert_close_rows, bf16_half_ulp, check_canary, lib_option, padded
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -184,7 +184,7 @@ def test_w4a4_gemm_exact_accumulators_and_output(m, k, n, g, bias):
 
 
 @pytest.mark.parametrize("m,k,n", [(333, 4096, 1024), (100, 512, 256), (700, 1024, 512)])
-def test_w4a4_cta_pair_variant(m, k, n, monkeypatch):
+def test_w4a4_cta_pair_variant(m, k, n):
     """The opt-in CTA-pair kernel (tcgen05 cta_group::2): the same integer group sums and output bits."""
     g = 128
     x, w, b = _w4a4_case(m, k, n, g, seed=m + k + 1, bias=True)
@@ -196,14 +196,14 @@ def test_w4a4_cta_pair_variant(m, k, n, monkeypatch):
     lq.load_quantized_params(sw2, torch.zeros_like(sw2), pw2)
     lq.bias = b.to(DEV)
     y_single = lq(x.to(DEV))
-    monkeypatch.setenv("ASRQ_B200_W4A4_PAIR", "1")
-    acc = torch.full((m, n, k // g), -12345, dtype=torch.int32, device=DEV)
-    y_pair = lq(x.to(DEV), acc_dump=acc)
-    asrq_b200.check_status()
-    assert torch.equal(acc.cpu(), acc_ref), "int32 group accumulators differ (pair kernel)"
-    assert torch.equal(y_pair, y_single)
-    lq.operand = "int8" if lq.operand == "f8" else "f8"
-    assert torch.equal(lq(x.to(DEV)), y_single)
+    with lib_option("w4a4_pair", 1):
+        acc = torch.full((m, n, k // g), -12345, dtype=torch.int32, device=DEV)
+        y_pair = lq(x.to(DEV), acc_dump=acc)
+        asrq_b200.check_status()
+        assert torch.equal(acc.cpu(), acc_ref), "int32 group accumulators differ (pair kernel)"
+        assert torch.equal(y_pair, y_single)
+        lq.operand = "int8" if lq.operand == "f8" else "f8"
+        assert torch.equal(lq(x.to(DEV)), y_single)
 
 
 def test_w4a4_tracks_unquantised_product():
@@ -216,3 +216,101 @@ def test_w4a4_tracks_unquantised_product():
     y_true = x.float() @ w.t()
     rel = float((y - y_true).norm() / y_true.norm())
     assert rel < 0.25, rel
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_config2_full_size(dtype):
+    """The W4A4 benchmark configuration at its own size: M=6000 tokens, K=4096, N=1024, g128, Student-t(4)
+    activations with 8 outlier channels x20.  Heavy tails are where the division-free quantiser takes its
+    exact-division branch.  Codes and scales bit-exact for every token; int32 group sums bit-exact and
+    output within the bar on a sample of 640 rows."""
+    c = O.make_c2(seed=0)
+    x = c["x"].to(dtype)
+    m, k = x.shape
+    n, g = c["w_fp"].shape[0], c["group_size"]
+    qa_ref, sa_ref, pa_ref = O.hadamard_quant_int4(x, True)
+    codes, sw, pw = O.prepare_w4a4_weight(c["w_fp"], g, True)
+    lq = asrq_b200.LinearQQ(k, n, 4, 4, g, bias=True, hadamard=True).to(DEV)
+    lq.load_quantized_params(sw, torch.zeros_like(sw), pw)
+    lq.bias = c["bias"].to(DEV)
+    xd = x.to(DEV)
+    qa, sa = _quant_gpu(x, True, dtype)
+    assert torch.equal(sa, sa_ref), "per-token scales differ"
+    assert torch.equal(qa, pa_ref), "packed activation codes differ"
+    gen = torch.Generator().manual_seed(1)
+    rows = torch.unique(torch.cat([torch.arange(0, 64), torch.arange(m - 64, m),
+                                   torch.randint(0, m, (512,), generator=gen)]))
+    acc = padded((m, n, k // g), torch.int32)
+    y = lq(xd, acc_dump=acc)
+    asrq_b200.check_status()
+    check_canary(acc, "acc_dump")
+    acc_ref = O.int4_group_accumulators(qa_ref[rows], codes, g)
+    assert torch.equal(acc[rows.to(DEV)].cpu(), acc_ref), "int32 group accumulators differ"
+    y_ref = O.w4a4_forward_fp32(qa_ref[rows], sa_ref[rows], codes, sw, c["bias"], g)
+    extra = bf16_half_ulp(y_ref) if dtype == torch.bfloat16 else None
+    assert_close_rows(y[rows.to(DEV)], y_ref, extra=extra, what=f"W4A4 M=6000 {dtype}")
+    assert torch.equal(lq(xd), y)   # the timed path (no dump) gives the same bits
+
+
+@pytest.mark.parametrize("g", [256, 512, 1024])
+@pytest.mark.parametrize("family", ["f8", "int8"])
+def test_tensor_core_group_sums_exact_for_wide_groups(g, family):
+    """Wide weight groups on the tcgen05 kernel with the largest possible sums: all codes -8 x -8
+    (sum 64 * g) and alternating +7 / -8.  The f8 family relies on the tensor core accumulating
+    kind::f8f6f4 products exactly in fp32 up to 2^16; both families must dump the exact integers."""
+    m, n, k = 128, 128, 2048
+    gen = torch.Generator().manual_seed(g)
+    qa = torch.full((m, k), -8, dtype=torch.int64)
+    qw = torch.full((n, k), -8, dtype=torch.int64)
+    qa[1::2] = torch.where(torch.arange(k) % 2 == 0, 7, -8)
+    qw[1::2] = 7
+    qa[m // 2:] = torch.randint(-8, 8, (m - m // 2, k), generator=gen)
+    qw[n // 2:] = torch.randint(-8, 8, (n - n // 2, k), generator=gen)
+    acc_ref = torch.einsum("mgk,ngk->mng", qa.reshape(m, -1, g), qw.reshape(n, -1, g)).to(torch.int32)
+    sw = torch.ones(n, k // g, dtype=torch.float16)
+    sa = torch.ones(m, dtype=torch.float32)
+    pa, pw = O.pack_signed_int4(qa).to(DEV), O.pack_signed_int4(qw).to(DEV)
+    a8 = torch.empty(m, k, dtype=torch.uint8, device=DEV)
+    w8 = torch.empty(n, k, dtype=torch.uint8, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    prep = "asrq_w4a4_prepare_weight_f8" if family == "f8" else "asrq_w4a4_prepare_weight"
+    _lib.call(prep, pw.data_ptr(), w8.data_ptr(), n, k, st)     # the same nibble -> operand expansion serves both sides
+    _lib.call(prep, pa.data_ptr(), a8.data_ptr(), m, k, st)
+    y = torch.empty(m, n, dtype=torch.float16, device=DEV)
+    acc = padded((m, n, k // g), torch.int32)
+    ws = torch.zeros(4096, dtype=torch.uint8, device=DEV)
+    _lib.call(f"asrq_w4a4_gemm_{family}", a8.data_ptr(), sa.to(DEV).data_ptr(), w8.data_ptr(), sw.to(DEV).data_ptr(),
+              None, y.data_ptr(), acc.data_ptr(), m, n, k, g, _lib.F16, ws.data_ptr(), ws.numel(), st)
+    _lib.call("asrq_check_status", ws.data_ptr(), st)
+    check_canary(acc, "acc_dump")
+    assert torch.equal(acc.cpu(), acc_ref), f"group sums differ for g={g} ({family})"
+
+
+@pytest.mark.parametrize("k", [1024, 4096])
+def test_w4a4_against_reference_composed_fixture(k):
+    """The layer assembled from the reference's own functions (tests/golden/make_golden.py: matmul_hadU,
+    RTNQuantizer, the activation fake-quant patch, F.linear): output within 2e-3 of the row maximum."""
+    d = np.load(os.path.join(GOLDEN, f"w4a4_composite_k{k}.npz"))
+    x = torch.from_numpy(d["x"].view(np.float16).copy())
+    w, g = torch.from_numpy(d["w"]), int(d["group_size"])
+    bias = torch.from_numpy(d["bias"].view(np.float16).copy())
+    n = w.shape[0]
+    pw, sw = asrq_b200.pack_w4a4(w, g, True)
+    assert np.array_equal(O.unpack_signed_int4(pw).numpy(), d["w_codes"])
+    lq = asrq_b200.LinearQQ(k, n, 4, 4, g, bias=True, hadamard=True).to(DEV)
+    lq.load_quantized_params(sw, torch.zeros_like(sw), pw)
+    lq.bias = bias.to(DEV)
+    y = lq(x.to(DEV))
+    assert_close_rows(y, torch.from_numpy(d["y"]), what=f"reference-composed W4A4 K={k}")
+    xr = x.repeat(8, 1)   # 72 / 192 tokens: the tensor-core kernel instead of the register-tile one
+    y2 = lq(xr.to(DEV))
+    assert_close_rows(y2, torch.from_numpy(d["y"]).repeat(8, 1), what=f"reference-composed W4A4 K={k}, tcgen05 path")
+
+
+def test_w4a4_gemm_rejects_bad_group_size():
+    p = torch.zeros(4096, dtype=torch.uint8, device=DEV)
+    for gs in (0, -128):
+        with pytest.raises(_lib.AsrqError) as e:
+            _lib.call("asrq_w4a4_gemm", p.data_ptr(), p.data_ptr(), p.data_ptr(), p.data_ptr(), None, p.data_ptr(), None,
+                      8, 64, 128, gs, _lib.F16, p.data_ptr(), p.numel(), None)
+        assert e.value.code == -2

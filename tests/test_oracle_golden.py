@@ -125,3 +125,32 @@ def test_w4a4_composite_consistency():
     # 4-bit x 4-bit is coarse, but must track the unquantised product
     y_true = x.float() @ w.t()
     assert float((y - y_true).abs().max()) < 0.35 * float(y_true.abs().max())
+
+
+@pytest.mark.parametrize("k", [1024, 4096])
+def test_w4a4_composite_against_reference_functions(k):
+    """The W4A4 layer assembled out of the reference's own functions (matmul_hadU in fp32 on both
+    operands, RTNQuantizer symmetric int4 g128 on the rotated weight, the activation fake-quant patch
+    around F.linear) against the integer composite of the oracle.
+
+    Every intermediate is bit-equal: rotated activations, weight codes and (fp32) weight scales.  With
+    fp32 weight scales the two results differ only by float summation order: bound 1e-5 of the row
+    maximum (measured 6e-7).  With the scales rounded to fp16, as LinearQ stores them
+    (asrq/core/linear.py:21-25), the bound is 0.5e-3 of the row maximum (measured 0.37e-3), a quarter
+    of the 2e-3 output bar."""
+    d = np.load(os.path.join(GOLDEN, f"w4a4_composite_k{k}.npz"))
+    x = torch.from_numpy(d["x"].view(np.float16).copy())
+    w, g = torch.from_numpy(d["w"]), int(d["group_size"])
+    bias = torch.from_numpy(d["bias"].view(np.float16).copy())
+    y_ref = torch.from_numpy(d["y"])
+    assert np.array_equal(O.hadamard_pow2(x.float()).numpy(), d["v"])
+    qa, sa, _ = O.hadamard_quant_int4(x, True)
+    codes, sw16, _ = O.prepare_w4a4_weight(w, g, True)
+    assert np.array_equal(codes.to(torch.int8).numpy(), d["w_codes"])
+    sw32 = torch.from_numpy(d["w_scales"])
+    assert torch.equal(sw16, sw32.half())
+    rowmax = y_ref.abs().max(dim=-1, keepdim=True).values
+    y32 = O.w4a4_forward_fp32(qa, sa, codes, sw32, bias, g)
+    assert float(((y32 - y_ref).abs() / rowmax).max()) < 1e-5
+    y16 = O.w4a4_forward_fp32(qa, sa, codes, sw16, bias, g)
+    assert float(((y16 - y_ref).abs() / rowmax).max()) < 0.5e-3

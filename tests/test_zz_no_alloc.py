@@ -16,17 +16,23 @@ from tests.gpu_util import DEV, assert_close_rows, run_a16_abi
 pytestmark = pytest.mark.gpu
 
 
-def _static_call(case):
+def _static_call(case, expect_no_allocation=False):
     x = case["x"].to(DEV).contiguous()
     m, k = x.shape
     n = case["weight"].shape[0]
     w, s, z = case["weight"].to(DEV), case["scales"].to(DEV), case["zeros"].to(DEV)
     b = None if case["bias"] is None else case["bias"].to(DEV)
     y = torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(DEV)[0]      # device-wide free bytes (cudaMemGetInfo)
     _lib.call("asrq_w4a16_gemv_static", x.data_ptr(), w.data_ptr(), s.data_ptr(), z.data_ptr(),
               None if b is None else b.data_ptr(), y.data_ptr(), m, n, k, case["group_size"], _lib.F16,
               torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    if expect_no_allocation:
+        # nothing between the two readings goes through torch's allocator, so any difference would be
+        # device memory taken by the entry point itself
+        assert torch.cuda.mem_get_info(DEV)[0] == free_before, "the static-scratch entry point allocated device memory"
     return y
 
 
@@ -42,6 +48,23 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
             assert_close_rows(y_st, ref32, what=f"static entry, round {rnd}")
             scale = ref32.abs().max(dim=-1, keepdim=True).values
             assert float(((y_st.float().cpu() - y_ws.float().cpu()).abs() / scale).max()) < 2e-3
+
+
+def test_static_scratch_entry_allocates_nothing_and_takes_bias_and_row_blocks():
+    """After a first call (which looks the array's address up), a call leaves the device's free memory
+    exactly as it found it.  With a bias, and with 20 tokens: two launches of 16 and 4 rows that share
+    the scratch array one after the other."""
+    gen = torch.Generator().manual_seed(23)
+    case = O.make_c3(seed=23, m=20, k=6144, n=2048, bits=4, group_size=64)
+    case["bias"] = (torch.randn(2048, generator=gen) * 0.02).half()
+    ref32 = O.linearq_forward_fp32(case["x"], case["weight"], case["scales"], case["zeros"], case["bias"], 4, 64)
+    _static_call(case)                                       # first call on this device: set-up
+    for _ in range(2):
+        y = _static_call(case, expect_no_allocation=True)
+        assert_close_rows(y, ref32, what="static entry, bias, 20 tokens")
+    y_ws = run_a16_abi("asrq_w4a16_gemv", case)
+    scale = ref32.abs().max(dim=-1, keepdim=True).values
+    assert float(((y.float().cpu() - y_ws.float().cpu()).abs() / scale).max()) < 2e-3
 
 
 def test_static_scratch_entry_rejects_large_n():
