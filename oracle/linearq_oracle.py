@@ -367,3 +367,39 @@ def make_c3(seed, m, k, n, bits, group_size=64, dtype=torch.float16):
 def row_tolerance(y_ref_fp32: torch.Tensor, rel: float = 2e-3) -> torch.Tensor:
     """Per-row absolute tolerance rel*||row||_inf of the fp32 CPU result, shape (M,1)."""
     return rel * y_ref_fp32.abs().max(dim=-1, keepdim=True).values
+
+
+# ----------------------------------------------------------------------------
+# Module form of the restatement (whole-model CPU baseline when the reference's files are not staged)
+# ----------------------------------------------------------------------------
+
+
+class PortLinearQ(torch.nn.Module):
+    """``LinearQ`` as the reference runs it on the CPU: dequantize the whole weight on every call, then
+    ``torch.matmul`` (asrq/core/linear.py:10-66), on top of the functions above."""
+
+    def __init__(self, in_features, out_features, bits, group_size=128, bias=True):
+        super().__init__()
+        self.in_features, self.out_features, self.bits, self.group_size = in_features, out_features, bits, group_size
+        self.register_buffer("weight", torch.zeros((out_features, in_features // (8 // bits)), dtype=torch.uint8))
+        self.register_buffer("bias", torch.zeros(out_features, dtype=torch.float16) if bias else None)
+        ng = (in_features + group_size - 1) // group_size
+        self.register_buffer("scales", torch.zeros((out_features, ng), dtype=torch.float16))
+        self.register_buffer("zeros", torch.zeros((out_features, ng), dtype=torch.float16))
+
+    def forward(self, x):
+        shape = x.shape
+        y = linearq_forward(x.reshape(-1, shape[-1]), self.weight, self.scales, self.zeros, self.bias, self.bits,
+                            self.group_size)
+        return y.reshape(*shape[:-1], self.out_features)
+
+
+def swap_in_port_linearq(model, bits, group_size, skip=()):
+    """Replaces every ``nn.Linear`` of ``model`` (except names ending in ``skip``) by an empty PortLinearQ."""
+    for name, mod in list(model.named_modules()):
+        for cname, child in list(mod.named_children()):
+            full = f"{name}.{cname}" if name else cname
+            if type(child) is torch.nn.Linear and not any(full == s or full.endswith("." + s) for s in skip):
+                setattr(mod, cname, PortLinearQ(child.in_features, child.out_features, bits, group_size,
+                                                bias=child.bias is not None))
+    return model
