@@ -20,7 +20,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libasrq_b200.so")
 OBJ_DIR = os.path.join(PKG, "build")
 
-SOURCES = ["api.cu", "gemv_a16.cu", "gemv_a16_splitk.cu", "gemm_a16_tc.cu", "gemm_a16_tc2.cu", "act_quant.cu", "w4a4_mma.cu", "w4a4_tc.cu"]
+SOURCES = ["api.cu", "gemv_a16.cu", "gemv_a16_splitk.cu", "gemv_a16_staged.cu", "gemm_a16_tc.cu", "gemm_a16_tc2.cu", "act_quant.cu", "w4a4_mma.cu", "w4a4_tc.cu"]
 HEADERS = ["common.cuh", "tcgen05.cuh", "dequant.cuh", os.path.join("..", "..", "include", "asrq_b200.h")]
 
 NVCC_FLAGS = [
@@ -48,7 +48,9 @@ def _newer(target: str, deps) -> bool:
     return all(os.path.getmtime(d) <= t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """``trace`` compiles with -DASRQ_TRACE: kernels record pipeline clock marks into the workspace when the
+    library option "trace" is set (a development build; the shipped library carries no trace code)."""
     nvcc = find_nvcc()
     os.makedirs(OBJ_DIR, exist_ok=True)
     headers = [os.path.normpath(os.path.join(CSRC, h)) for h in HEADERS]
@@ -60,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs.append(o)
         if not force and _newer(o, [s] + headers):
             continue
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+        cmd = [nvcc] + NVCC_FLAGS + (["-DASRQ_TRACE"] if trace else []) + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, pr in procs:
         out, _ = pr.communicate()
@@ -77,5 +79,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv or "--trace" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv)
     print(path)

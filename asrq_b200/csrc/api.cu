@@ -70,7 +70,7 @@ struct OptionDef {
   int def;
 };
 const OptionDef kOptionDefs[kOptCount] = {
-    {"no_pdl", 0},      {"gemv_kernel", 0}, {"gemv_cpw", 0},  {"gemv_loop", -1},   {"tc_split", 0},   {"tc_bt", 0},
+    {"no_pdl", 0},      {"gemv_kernel", 0}, {"gemv_cpw", 0},  {"gemv_xstage", 1}, {"gemv_loop", -1},   {"tc_split", 0},   {"tc_bt", 0},
     {"tc_pair", -1},    {"tc_pair_release", 0}, {"w4a4_bt", 0}, {"w4a4_pair", -1}, {"trace", 0},      {"trace_block", 0},
 };
 struct OptionTable {

@@ -35,6 +35,7 @@ enum Option {
   kOptNoPdl = 0,     // 1: launch without programmatic dependent launch
   kOptGemvKernel,    // decode kernel: 0 auto, 1 strip-per-block (registers), 2 split-K (workspace), 3 staged (shared memory)
   kOptGemvCpw,       // strip-per-block decode kernel: steps per warp (0 auto)
+  kOptGemvXStage,    // staged decode kernel: 0 = fragment loads of the activations straight from L2 (no staging in shared memory)
   kOptGemvLoop,      // strip-per-block decode kernel, rounds variant: -1 auto, 0 never, 1 whenever a layer needs > 1 wave
   kOptTcSplit,       // prefill kernel: 1 disables split K
   kOptTcBt,          // prefill kernels: token-tile width (0 auto)

@@ -221,8 +221,10 @@ int asrq_w4a4_gemm_f8(const uint8_t* a8, const float* sa, const uint8_t* w8, con
  * environment variable ASRQ_B200_<NAME IN UPPER CASE>, read once when the library is first used;
  * afterwards only asrq_set_option changes it (no call path reads the environment).  Options:
  *   no_pdl (0)            1: launch every kernel without programmatic dependent launch
- *   gemv_kernel (0)       decode kernel: 0 auto, 1 strip per block, 2 split K through the workspace,
- *                         3 weights staged in shared memory ahead of the stream dependency
+ *   gemv_kernel (0)       decode kernel: 0 auto (strip per block, split K for shapes outside its menu),
+ *                         1 strip per block, 2 split K through the workspace, 3 weights staged in
+ *                         shared memory ahead of the stream dependency (measured no faster; opt-in)
+ *   gemv_xstage (1)       staged decode kernel: 0 = activations read from L2 per fragment, not staged
  *   gemv_cpw (0), gemv_loop (-1)   strip-per-block decode kernel: steps per warp, rounds variant
  *   tc_split (0)          1: no split K in the prefill kernel
  *   tc_bt (0), w4a4_bt (0)         token-tile width of the tcgen05 kernels (0 auto)

@@ -376,3 +376,79 @@ def test_module_on_non_current_device():
     y = lq(case["x"].to(dev1))
     assert y.device == dev1
     assert_close_rows(y, _ref32(case), what="layer on cuda:1, current device cuda:0")
+
+
+@pytest.mark.parametrize("bits,g,m,k,n,bias,dtype", [
+    (4, 64, 1, 2048, 6144, False, torch.float16),    # decode-sweep shapes, three tiles per block
+    (4, 64, 16, 6144, 2048, False, torch.float16),   # one 48 KB tile per block, K split over all warps
+    (2, 64, 8, 2048, 4096, False, torch.float16),
+    (2, 64, 16, 6144, 2048, True, torch.float16),
+    (4, 128, 32, 1280, 1280, True, torch.float16),   # whole-model decode batch: two token groups, one launch
+    (4, 128, 32, 1280, 3840, True, torch.float16),   # fused q/k/v
+    (4, 128, 32, 5120, 1280, True, torch.float16),
+    (4, 128, 17, 1280, 5120, True, torch.bfloat16),  # ragged second token group
+    (4, 128, 40, 1280, 1280, False, torch.float16),  # > 32 tokens: two launches
+    (4, 32, 3, 256, 48, True, torch.float16),        # four groups per step, three tiles on three blocks
+    (2, 256, 5, 512, 64, False, torch.float16),
+    (4, 128, 4, 384, 4096, False, torch.float16),    # row bytes not a multiple of 128
+])
+def test_gemv_staged_kernel(bits, g, m, k, n, bias, dtype):
+    """The staged decode kernel (weights prefetched into shared memory ahead of the stream dependency)
+    against the fp32 CPU result, and against the strip-per-block kernel it replaces."""
+    gen = torch.Generator().manual_seed(bits * 31 + m + n)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen).to(dtype), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half() if bias else None,
+                bits=bits, group_size=g)
+    with lib_option("gemv_kernel", 3):
+        y = run_a16_abi(f"asrq_w{bits}a16_gemv", case, dtype=dtype)
+        y2 = run_a16_abi(f"asrq_w{bits}a16_gemv", case, dtype=dtype)
+    with lib_option("gemv_kernel", 1):
+        y_old = run_a16_abi(f"asrq_w{bits}a16_gemv", case, dtype=dtype)
+    ref = _ref32(case, dtype)
+    extra = bf16_half_ulp(ref) if dtype == torch.bfloat16 else None
+    assert_close_rows(y, ref, extra=extra, what=f"staged gemv w{bits} g{g} m{m} {k}x{n}")
+    assert_close_rows(y_old, ref, extra=extra, what=f"strip gemv w{bits} g{g} m{m} {k}x{n}")
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("m", [1, 16, 32])
+def test_decode_chain_orders_dependent_launches(m):
+    """A chain of layers in which every launch consumes the previous launch's output, replayed as one CUDA
+    graph: launches prefetch their weights before they wait for their predecessor, and must still see its
+    output.  Same bits as the chain run without programmatic dependent launch."""
+    gen = torch.Generator().manual_seed(m)
+    d = 1280
+    layers = []
+    for i in range(6):
+        w = torch.randn(d, d, generator=gen) * (1.0 / d ** 0.5)
+        codes, scales, zeros, _ = O.rtn_codes(w, 4, 128, False)
+        layers.append(make_layer(dict(x=torch.zeros(1, d), weight=O.pack_codes(codes, 4), scales=scales.half(),
+                                      zeros=zeros.half(), bias=None, bits=4, group_size=128)))
+    x = torch.randn(m, d, generator=gen).half().to(DEV)
+
+    def chain():
+        h = x
+        for L in layers:
+            h = L(h)
+        return h
+    with lib_option("no_pdl", 1):
+        ref = chain().clone()
+    torch.cuda.synchronize()
+    eager = chain().clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = chain()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(20):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(eager, ref) and torch.equal(out, ref)
+    import asrq_b200
+    asrq_b200.check_status()
