@@ -39,6 +39,10 @@ int w4a4_gemm_int8(const uint8_t* w8, const uint8_t* a8, const float* sa, const 
                    int32_t* acc_dump, int64_t M, int64_t N, int64_t K, int group_size, int dtype, int fmt,
                    void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
 size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
+bool gemm_a16_skinny_supports(int64_t M, int64_t N, int64_t K, int group_size, int sm_count, size_t workspace_bytes);
+int gemm_a16_skinny(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
+                    void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
+                    size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 // ---- errors -----------------------------------------------------------------------------
 std::string& last_error() {
@@ -70,7 +74,7 @@ struct OptionDef {
   int def;
 };
 const OptionDef kOptionDefs[kOptCount] = {
-    {"no_pdl", 0},      {"gemv_kernel", 0}, {"gemv_cpw", 0},  {"gemv_xstage", 1}, {"gemv_loop", -1},   {"tc_split", 0},   {"tc_bt", 0},
+    {"no_pdl", 0},      {"mid_kernel", 0}, {"gemv_kernel", 0}, {"gemv_cpw", 0},  {"gemv_xstage", 1}, {"gemv_loop", -1},   {"tc_split", 0},   {"tc_bt", 0},
     {"tc_pair", -1},    {"tc_pair_release", 0}, {"w4a4_bt", 0}, {"w4a4_pair", -1}, {"trace", 0},      {"trace_block", 0},
 };
 struct OptionTable {
@@ -298,6 +302,11 @@ static int a16_gemm(int bits, const void* x, const uint8_t* w, const void* scale
   const DeviceFacts* f;
   if ((rc = device_facts(&f))) return rc;
   if (M == 0) return ASRQ_OK;
+  // decode batches (17..64 tokens): the chain-oriented tensor-core kernel where its one-wave grid fits
+  if (M <= 64 && option(kOptMidKernel) != 1 && (reinterpret_cast<uintptr_t>(bias) & 7u) == 0 &&
+      gemm_a16_skinny_supports(M, N, K, group_size, f->sm_count, workspace_bytes))
+    return gemm_a16_skinny(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
+                           f->sm_count, static_cast<cudaStream_t>(stream));
   return gemm_a16_tc(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
                      f->sm_count, static_cast<cudaStream_t>(stream));
 }
@@ -331,6 +340,13 @@ int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scal
     return fail(ASRQ_ERR_SHAPE, "asrq_linearq_a16: bits must be 2 or 4 (got %d)", bits);
   }
   const bool tc_ok = N % 128 == 0 && K % 64 == 0 && group_size > 0 && group_size % 64 == 0 && K % group_size == 0;
+  // 17..32 tokens: the tensor cores (gemm_a16_skinny.cu) unless switched off; the mma.sync decode kernel is bound
+  // by the legacy MMA pipe there
+  if (M > 16 && M <= kGemvMaxM && tc_ok && option(kOptMidKernel) != 1 && workspace && bits != 0) {
+    int sms = 0;
+    if (current_device_sm_count(&sms) == ASRQ_OK && gemm_a16_skinny_supports(M, N, K, group_size, sms, workspace_bytes))
+      return a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+  }
   if (M > kGemvMaxM && tc_ok)
     return a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
   return a16_gemv(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);

@@ -33,6 +33,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // No launch path calls getenv.
 enum Option {
   kOptNoPdl = 0,     // 1: launch without programmatic dependent launch
+  kOptMidKernel,     // 17..64 tokens: 0 auto (chain-oriented tensor-core kernel where it fits), 1 the decode / prefill kernels
   kOptGemvKernel,    // decode kernel: 0 auto, 1 strip-per-block (registers), 2 split-K (workspace), 3 staged (shared memory)
   kOptGemvCpw,       // strip-per-block decode kernel: steps per warp (0 auto)
   kOptGemvXStage,    // staged decode kernel: 0 = fragment loads of the activations straight from L2 (no staging in shared memory)

@@ -221,6 +221,8 @@ int asrq_w4a4_gemm_f8(const uint8_t* a8, const float* sa, const uint8_t* w8, con
  * environment variable ASRQ_B200_<NAME IN UPPER CASE>, read once when the library is first used;
  * afterwards only asrq_set_option changes it (no call path reads the environment).  Options:
  *   no_pdl (0)            1: launch every kernel without programmatic dependent launch
+ *   mid_kernel (0)        17..64 tokens: 0 = the chain-oriented tensor-core kernel where its grid fits one wave,
+ *                         1 = the decode kernel (<= 32 tokens) / the prefill kernel instead
  *   gemv_kernel (0)       decode kernel: 0 auto (strip per block, split K for shapes outside its menu),
  *                         1 strip per block, 2 split K through the workspace, 3 weights staged in
  *                         shared memory ahead of the stream dependency (measured no faster; opt-in)

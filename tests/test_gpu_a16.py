@@ -452,3 +452,44 @@ def test_decode_chain_orders_dependent_launches(m):
     assert torch.equal(eager, ref) and torch.equal(out, ref)
     import asrq_b200
     asrq_b200.check_status()
+
+
+@pytest.mark.parametrize("bits,g,m,k,n,bias,dtype", [
+    (4, 128, 32, 1280, 1280, True, torch.float16),    # whole-model decode batch: 10 tiles x 8 K parts
+    (4, 128, 32, 1280, 3840, True, torch.float16),    # fused q/k/v: 30 tiles x 4 parts
+    (4, 128, 32, 1280, 5120, True, torch.float16),    # 40 tiles x 3 parts
+    (4, 128, 32, 5120, 1280, True, torch.float16),    # long K: 12 parts of 6-7 K blocks
+    (4, 128, 17, 1280, 1280, False, torch.bfloat16),  # ragged token tile
+    (4, 128, 64, 1280, 5120, True, torch.float16),    # 64-token tile
+    (4, 128, 50, 1024, 4096, False, torch.float16),
+    (2, 64, 24, 512, 256, True, torch.float16),       # one K block per part
+    (2, 128, 33, 2048, 1024, False, torch.bfloat16),
+    (4, 64, 20, 64, 128, True, torch.float16),        # a single K block, a single tile, no split
+])
+def test_mid_m_tensor_core_kernel(bits, g, m, k, n, bias, dtype):
+    """17..64 tokens on the chain-oriented tcgen05 kernel (weights fetched and unpacked ahead of the stream
+    dependency, K parts meeting through the workspace) against the fp32 CPU result; two runs give the same
+    bits and the tile counters come back to zero (checked by the call helper); against the kernels it replaces."""
+    from asrq_b200 import _lib
+    gen = torch.Generator().manual_seed(bits * 17 + m + n)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    codes, scales, zeros, _ = O.rtn_codes(w, bits, g, False)
+    case = dict(x=torch.randn(m, k, generator=gen).to(dtype), weight=O.pack_codes(codes, bits), scales=scales.half(),
+                zeros=zeros.half(), bias=(torch.randn(n, generator=gen) * 0.02).half() if bias else None,
+                bits=bits, group_size=g)
+    ref = _ref32(case, dtype)
+    y = run_a16_abi(f"asrq_w{bits}a16_gemm", case, dtype=dtype)
+    y2 = run_a16_abi(f"asrq_w{bits}a16_gemm", case, dtype=dtype)
+    assert torch.equal(y, y2)
+    if dtype == torch.float16:
+        assert_close_rows(y, ref, what=f"mid-M w{bits} m{m} {k}x{n}")
+    else:
+        wd = O.dequantize_weight(case["weight"], case["scales"], case["zeros"], bits, g, k, torch.float32)
+        xf = case["x"].float()
+        w_round = 6.0 * 2.0 ** -9 / 3 ** 0.5 * torch.sqrt((xf * xf) @ (wd * wd).t())
+        assert_close_rows(y, ref, rel=2e-3, extra=bf16_half_ulp(ref) + w_round, what=f"mid-M bf16 w{bits} m{m} {k}x{n}")
+    if m >= 32:
+        with lib_option("mid_kernel", 1):
+            y_old = run_a16_abi(f"asrq_w{bits}a16_gemm", case, dtype=dtype)
+        scale = ref.abs().max(dim=-1, keepdim=True).values
+        assert float(((y.float().cpu() - y_old.float().cpu()).abs() / scale).max()) < 4e-3
