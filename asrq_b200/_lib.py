@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_PKG, "libasrq_b200.so")
 F16, BF16 = 0, 1
 WS_A16_GEMV, WS_A16_GEMM, WS_W4A4_GEMM, WS_LINEARQ = 1, 2, 3, 4
 STATUS_BYTES = 256
+ACT_NONE, ACT_GELU = 0, 1
 
 
 class AsrqError(RuntimeError):
@@ -51,6 +52,10 @@ SIGNATURES = {
     "asrq_w4a16_gemm": (c_int, _A16_ARGS),
     "asrq_w2a16_gemm": (c_int, _A16_ARGS),
     "asrq_linearq_a16": (c_int, [c_int] + _A16_ARGS),
+    "asrq_linearq_a16_fused": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                       c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "asrq_add_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p, c_void_p, c_int64,
+                                   c_int64, c_int, c_void_p]),
     "asrq_hadamard_quant_int4": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
     "asrq_w4a4_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),

@@ -21,7 +21,10 @@ size_t gemv_workspace_bytes(int64_t N);
 size_t gemm_tc_workspace_bytes(int64_t M, int64_t N);
 int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep, bool* fused);
+int add_layernorm(const void* x, const void* delta, const void* gamma, const void* beta, float eps, void* x_out, void* h_out,
+                  int64_t rows, int64_t dim, int dtype, cudaStream_t stream);
+int epilogue16_apply(void* y, const void* residual, int64_t M, int64_t N, int act, int dtype, int sm_count, cudaStream_t stream);
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
                         int out_int8, cudaStream_t stream);
 int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void* bias, void* y, int64_t M, int64_t N,
@@ -42,7 +45,7 @@ size_t w4a4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool gemm_a16_skinny_supports(int64_t M, int64_t N, int64_t K, int group_size, int sm_count, size_t workspace_bytes);
 int gemm_a16_skinny(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                     void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                    size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                    size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep);
 
 // ---- errors -----------------------------------------------------------------------------
 std::string& last_error() {
@@ -294,8 +297,11 @@ static int a16_gemv(int bits, const void* x, const uint8_t* w, const void* scale
 
 static int a16_gemm(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                     void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                    size_t workspace_bytes, void* stream) {
+                    size_t workspace_bytes, void* stream, const Epilogue& ep = Epilogue(), bool* fused = nullptr) {
   last_error().clear();
+  bool fused_here = false;
+  if (!fused) fused = &fused_here;
+  *fused = false;
   int rc = check_a16_common(bits == 4 ? "asrq_w4a16_gemm" : "asrq_w2a16_gemm", x, w, scales, zeros, y, M, N, K, dtype,
                             workspace);
   if (rc) return rc;
@@ -304,11 +310,13 @@ static int a16_gemm(int bits, const void* x, const uint8_t* w, const void* scale
   if (M == 0) return ASRQ_OK;
   // decode batches (17..64 tokens): the chain-oriented tensor-core kernel where its one-wave grid fits
   if (M <= 64 && option(kOptMidKernel) != 1 && (reinterpret_cast<uintptr_t>(bias) & 7u) == 0 &&
-      gemm_a16_skinny_supports(M, N, K, group_size, f->sm_count, workspace_bytes))
+      gemm_a16_skinny_supports(M, N, K, group_size, f->sm_count, workspace_bytes)) {
+    *fused = true;
     return gemm_a16_skinny(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
-                           f->sm_count, static_cast<cudaStream_t>(stream));
+                           f->sm_count, static_cast<cudaStream_t>(stream), ep);
+  }
   return gemm_a16_tc(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
-                     f->sm_count, static_cast<cudaStream_t>(stream));
+                     f->sm_count, static_cast<cudaStream_t>(stream), ep, fused);
 }
 
 int asrq_w4a16_gemv(const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias, void* y,
@@ -332,24 +340,72 @@ int asrq_w2a16_gemm(const void* x, const uint8_t* w, const void* scales, const v
   return a16_gemm(2, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
 }
 
-int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
-                     const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
-                     void* workspace, size_t workspace_bytes, void* stream) {
+static int linearq_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                       const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                       void* workspace, size_t workspace_bytes, void* stream, const Epilogue& ep) {
   if (bits != 2 && bits != 4) {
     last_error().clear();
     return fail(ASRQ_ERR_SHAPE, "asrq_linearq_a16: bits must be 2 or 4 (got %d)", bits);
   }
+  const bool want_ep = ep.act != kActNone || ep.residual != nullptr;
+  if (ep.act != kActNone && ep.act != kActGelu) return fail(ASRQ_ERR_SHAPE, "asrq_linearq_a16_fused: act %d", ep.act);
+  if (want_ep && ((M * N) % 8 || !aligned16(y) || !aligned16(ep.residual)))
+    return fail(ASRQ_ERR_ALIGN, "asrq_linearq_a16_fused: y and residual must be 16-byte aligned and M*N a multiple of 8");
   const bool tc_ok = N % 128 == 0 && K % 64 == 0 && group_size > 0 && group_size % 64 == 0 && K % group_size == 0;
+  bool fused = false;
+  int rc;
   // 17..32 tokens: the tensor cores (gemm_a16_skinny.cu) unless switched off; the mma.sync decode kernel is bound
   // by the legacy MMA pipe there
-  if (M > 16 && M <= kGemvMaxM && tc_ok && option(kOptMidKernel) != 1 && workspace && bits != 0) {
+  bool mid = false;
+  if (M > 16 && M <= kGemvMaxM && tc_ok && option(kOptMidKernel) != 1 && workspace) {
     int sms = 0;
-    if (current_device_sm_count(&sms) == ASRQ_OK && gemm_a16_skinny_supports(M, N, K, group_size, sms, workspace_bytes))
-      return a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+    mid = current_device_sm_count(&sms) == ASRQ_OK && gemm_a16_skinny_supports(M, N, K, group_size, sms, workspace_bytes);
   }
-  if (M > kGemvMaxM && tc_ok)
-    return a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
-  return a16_gemv(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+  // Large M (the persistent CTA-pair kernel): its four epilogue warps run under the next tile's main loop
+  // and have no slack for an erf per output or for a strided read of the residual (measured: a Whisper
+  // encoder pass went from 95 to 195 ms with both fused), so the epilogue is a pass of its own there.
+  const Epilogue in_kernel = M <= 256 ? ep : Epilogue();
+  if (mid || (M > kGemvMaxM && tc_ok))
+    rc = a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream,
+                  in_kernel, &fused);
+  else
+    rc = a16_gemv(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
+  if (M > 256) fused = false;
+  if (rc || !want_ep || fused || M == 0) return rc;
+  // the kernel that ran does not fuse the epilogue: one more pass over the output
+  const DeviceFacts* f;
+  if ((rc = device_facts(&f))) return rc;
+  return epilogue16_apply(y, ep.residual, M, N, ep.act, dtype, f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                     const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  return linearq_a16(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream,
+                     Epilogue());
+}
+
+int asrq_linearq_a16_fused(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                           const void* bias, const void* residual, void* y, int64_t M, int64_t N, int64_t K,
+                           int group_size, int dtype, int act, void* workspace, size_t workspace_bytes, void* stream) {
+  Epilogue ep;
+  ep.residual = residual;
+  ep.act = act;
+  return linearq_a16(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream, ep);
+}
+
+int asrq_add_layernorm(const void* x, const void* delta, const void* gamma, const void* beta, float eps, void* x_out,
+                       void* h_out, int64_t rows, int64_t dim, int dtype, void* stream) {
+  last_error().clear();
+  if (!x || !gamma || !beta || !h_out) return fail(ASRQ_ERR_NULL, "asrq_add_layernorm: x, gamma, beta and h_out must not be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_add_layernorm: dtype %d", dtype);
+  if (rows < 0 || dim <= 0 || dim > (1 << 20) || rows > (int64_t(1) << 31) - 64)
+    return fail(ASRQ_ERR_SHAPE, "asrq_add_layernorm: rows=%lld dim=%lld", (long long)rows, (long long)dim);
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (rows == 0) return ASRQ_OK;
+  return add_layernorm(x, delta, gamma, beta, eps, x_out, h_out, rows, dim, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,

@@ -136,4 +136,29 @@ __device__ __forceinline__ uint16_t float_to_out16(float v, bool bf16) {
   return *reinterpret_cast<uint16_t*>(&h);
 }
 
+// ---- fused epilogue of a quantized layer -----------------------------------------------------------
+// What may follow y = x . W^T + bias inside the same kernel: an activation, or the addition of a residual
+// stream.  Both act on the 16-bit-rounded layer output, exactly as the unfused sequence of modules does
+// (the layer returns a 16-bit tensor; GELU, or the residual add, reads it and rounds again).
+constexpr int kActNone = 0, kActGelu = 1;  // GELU: x * Phi(x) with the exact erf form
+struct Epilogue {
+  const void* residual = nullptr;  // same shape and type as y, or NULL
+  int act = kActNone;
+};
+__device__ __forceinline__ float out16_to_float(uint16_t b, bool bf16) {
+  return bf16 ? bf16_bits_to_float(b) : __half2float(__ushort_as_half(b));
+}
+__device__ __forceinline__ uint16_t epilogue16(uint16_t y16, int act, bool has_res, uint16_t res16, bool bf16) {
+  float r = out16_to_float(y16, bf16);
+  if (act == kActGelu) y16 = float_to_out16(0.5f * r * (1.f + erff(r * 0.70710678118654752440f)), bf16);
+  if (has_res) y16 = float_to_out16(out16_to_float(res16, bf16) + out16_to_float(y16, bf16), bf16);
+  return y16;
+}
+// the fp32 result of a layer (bias already added) through rounding and the epilogue
+__device__ __forceinline__ uint16_t finish16(float v, int act, const uint16_t* residual, size_t idx, bool bf16) {
+  const uint16_t y16 = float_to_out16(v, bf16);
+  if (act == kActNone && residual == nullptr) return y16;
+  return epilogue16(y16, act, residual != nullptr, residual ? residual[idx] : uint16_t(0), bf16);
+}
+
 }  // namespace asrq

@@ -45,6 +45,8 @@ struct SkinnyParams {
   const __half* scales;
   const __half* zeros;
   const __half* bias;
+  const uint16_t* residual;  // fused epilogue: y = residual + layer output (NULL: none)
+  int act;                   // fused epilogue: activation on the layer output (kActNone / kActGelu)
   uint16_t* y;
   unsigned* status;
   float* partials;     // [tile][part][bt tokens][128 features]
@@ -210,7 +212,6 @@ gemm_a16_skinny_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_con
         tc::fence_after_sync();
         if (warp == 2 && lane == 0) SK_MARK(6);
         const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16);
-        uint16_t* yp = p.y + f;
         if (p.ksplit == 1) {
           for (int ch = 0; ch < p.bt / 32; ++ch) {
             uint32_t r[32];
@@ -218,7 +219,10 @@ gemm_a16_skinny_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_con
             tc::tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (ch * 32 + j < p.M) yp[size_t(ch * 32 + j) * p.N] = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+              if (ch * 32 + j < p.M) {
+                const size_t idx = size_t(ch * 32 + j) * p.N + f;
+                p.y[idx] = finish16(__uint_as_float(r[j]) + bias, p.act, p.residual, idx, BF16);
+              }
           }
         } else {
           // this block's part of the tile, fp32 [token][128 features]: a warp writes 128 contiguous bytes per token
@@ -271,10 +275,11 @@ gemm_a16_skinny_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_con
             const float2 b01 = __half22float2(u32_as_h2(b.x)), b23 = __half22float2(u32_as_h2(b.y));
             v.x += b01.x; v.y += b01.y; v.z += b23.x; v.w += b23.y;
           }
+          const size_t idx = size_t(tok) * p.N + f;
           uint2 out;
-          out.x = uint32_t(float_to_out16(v.x, BF16)) | (uint32_t(float_to_out16(v.y, BF16)) << 16);
-          out.y = uint32_t(float_to_out16(v.z, BF16)) | (uint32_t(float_to_out16(v.w, BF16)) << 16);
-          *reinterpret_cast<uint2*>(p.y + size_t(tok) * p.N + f) = out;
+          out.x = uint32_t(finish16(v.x, p.act, p.residual, idx, BF16)) | (uint32_t(finish16(v.y, p.act, p.residual, idx + 1, BF16)) << 16);
+          out.y = uint32_t(finish16(v.z, p.act, p.residual, idx + 2, BF16)) | (uint32_t(finish16(v.w, p.act, p.residual, idx + 3, BF16)) << 16);
+          *reinterpret_cast<uint2*>(p.y + idx) = out;
         }
       }
       if (threadIdx.x == 0) p.counters[ft] = 0u;
@@ -340,7 +345,7 @@ bool gemm_a16_skinny_supports(int64_t M, int64_t N, int64_t K, int group_size, i
 
 int gemm_a16_skinny(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                     void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                    size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                    size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep) {
   SkinnyPlan pl;
   if (!skinny_plan(M, N, K, group_size, sm_count, workspace_bytes, &pl))
     return fail(ASRQ_ERR_SHAPE, "w%da16 skinny gemm: unsupported shape M=%lld N=%lld K=%lld g=%d", bits, (long long)M,
@@ -350,6 +355,8 @@ int gemm_a16_skinny(int bits, const void* x, const uint8_t* w, const void* scale
   p.scales = static_cast<const __half*>(scales);
   p.zeros = static_cast<const __half*>(zeros);
   p.bias = static_cast<const __half*>(bias);
+  p.residual = static_cast<const uint16_t*>(ep.residual);
+  p.act = ep.act;
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
   p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + kPartialOffset);

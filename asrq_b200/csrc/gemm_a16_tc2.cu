@@ -33,6 +33,8 @@ struct GemmTc2Params {
   const __half* scales;
   const __half* zeros;
   const __half* bias;
+  const uint16_t* residual;  // fused epilogue: y = residual + layer output (NULL: none)
+  int act;                   // fused epilogue: activation on the layer output (kActNone / kActGelu)
   uint16_t* y;
   unsigned* status;
   int M, N, K, group_size, groups_per_row, bt, nstages, n_fpairs, n_ttiles;
@@ -281,13 +283,13 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         if (rows_left >= (ch + 1) * 32) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+            *yp = finish16(__uint_as_float(r[j]) + bias, p.act, p.residual, size_t(yp - p.y), BF16);
             yp += p.N;
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            if (ch * 32 + j < rows_left) *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+            if (ch * 32 + j < rows_left) *yp = finish16(__uint_as_float(r[j]) + bias, p.act, p.residual, size_t(yp - p.y), BF16);
             yp += p.N;
           }
         }
@@ -346,7 +348,7 @@ bool gemm_a16_tc2_supports(int64_t M, int64_t N, int64_t K, int group_size) {
 
 int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                  void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep) {
   if (!gemm_a16_tc2_supports(M, N, K, group_size))
     return fail(ASRQ_ERR_SHAPE, "w%da16 gemm (pair): unsupported shape N=%lld K=%lld g=%d", bits, (long long)N,
                 (long long)K, group_size);
@@ -358,6 +360,8 @@ int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, 
   p.scales = static_cast<const __half*>(scales);
   p.zeros = static_cast<const __half*>(zeros);
   p.bias = static_cast<const __half*>(bias);
+  p.residual = static_cast<const uint16_t*>(ep.residual);
+  p.act = ep.act;
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
   p.M = int(M);

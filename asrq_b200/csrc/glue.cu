@@ -1,0 +1,190 @@
+// The steps either side of a quantized layer in a decoder block, as kernels of their own:
+//
+//   add_layernorm   x' = x + delta (optional), h = LayerNorm(x') * gamma + beta, one warp per row, fp32
+//                   statistics on the 16-bit-rounded x' (what the unfused sequence "add, then layer_norm"
+//                   computes), 16-bit in and out;
+//   epilogue16      y = act(y) or y = residual + y on an already written output: the fall-back for
+//                   layers whose kernel does not fuse the epilogue (the tcgen05 kernels fuse it).
+//
+// Both open with griddepcontrol.launch_dependents / .wait and are launched with programmatic stream
+// serialisation, so in a chain of this library's kernels (a decoder step replayed as a CUDA graph)
+// consecutive launches overlap their ramp-up with the predecessor's tail.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace asrq {
+
+namespace {
+
+__device__ __forceinline__ float in16(uint16_t b, bool bf16) {
+  return bf16 ? bf16_bits_to_float(b) : __half2float(__ushort_as_half(b));
+}
+
+constexpr int kLnWarps = 8;
+
+// VEC: 16-byte vectors per lane (dim = 256 * VEC); generic dims take the strided loop with VEC = 0
+template <int VEC>
+__global__ void __launch_bounds__(32 * kLnWarps)
+add_layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ delta, const uint16_t* __restrict__ gamma,
+                     const uint16_t* __restrict__ beta, float eps, uint16_t* __restrict__ x_out, uint16_t* __restrict__ h_out,
+                     int rows, int dim, int bf16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kLnWarps + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t off = size_t(row) * dim;
+  if constexpr (VEC > 0) {
+    float v[VEC > 0 ? VEC * 8 : 1];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int e = (i * 32 + lane) * 8;
+      const uint4 a = *reinterpret_cast<const uint4*>(x + off + e);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      uint32_t dw[4] = {0, 0, 0, 0};
+      if (delta) {
+        const uint4 d = *reinterpret_cast<const uint4*>(delta + off + e);
+        dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w;
+      }
+      uint32_t ow[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo = in16(uint16_t(aw[j] & 0xffffu), bf16), hi = in16(uint16_t(aw[j] >> 16), bf16);
+        if (delta) {
+          lo += in16(uint16_t(dw[j] & 0xffffu), bf16);
+          hi += in16(uint16_t(dw[j] >> 16), bf16);
+        }
+        const uint16_t lo16 = float_to_out16(lo, bf16), hi16 = float_to_out16(hi, bf16);
+        ow[j] = uint32_t(lo16) | (uint32_t(hi16) << 16);
+        v[i * 8 + 2 * j] = in16(lo16, bf16);
+        v[i * 8 + 2 * j + 1] = in16(hi16, bf16);
+      }
+      if (x_out) *reinterpret_cast<uint4*>(x_out + off + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC * 8; ++i) sum += v[i];
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / float(dim);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC * 8; ++i) {
+      const float d = v[i] - mean;
+      sq = fmaf(d, d, sq);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / float(dim) + eps);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int e = (i * 32 + lane) * 8;
+      const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma + e));
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(beta + e));
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, bw[4] = {b.x, b.y, b.z, b.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = (v[i * 8 + 2 * j] - mean) * rstd * in16(uint16_t(gw[j] & 0xffffu), bf16) + in16(uint16_t(bw[j] & 0xffffu), bf16);
+        const float hi = (v[i * 8 + 2 * j + 1] - mean) * rstd * in16(uint16_t(gw[j] >> 16), bf16) + in16(uint16_t(bw[j] >> 16), bf16);
+        ow[j] = uint32_t(float_to_out16(lo, bf16)) | (uint32_t(float_to_out16(hi, bf16)) << 16);
+      }
+      *reinterpret_cast<uint4*>(h_out + off + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  } else {
+    // any dimension: three passes over the row (the second and third hit L1/L2)
+    float sum = 0.f;
+    for (int e = lane; e < dim; e += 32) {
+      float a = in16(x[off + e], bf16);
+      if (delta) a += in16(delta[off + e], bf16);
+      const uint16_t a16 = float_to_out16(a, bf16);
+      if (x_out) x_out[off + e] = a16;
+      sum += in16(a16, bf16);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / float(dim);
+    float sq = 0.f;
+    for (int e = lane; e < dim; e += 32) {
+      float a = in16(x[off + e], bf16);
+      if (delta) a += in16(delta[off + e], bf16);
+      const float d = in16(float_to_out16(a, bf16), bf16) - mean;
+      sq = fmaf(d, d, sq);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / float(dim) + eps);
+    for (int e = lane; e < dim; e += 32) {
+      float a = in16(x[off + e], bf16);
+      if (delta) a += in16(delta[off + e], bf16);
+      const float c = in16(float_to_out16(a, bf16), bf16);
+      h_out[off + e] = float_to_out16((c - mean) * rstd * in16(gamma[e], bf16) + in16(beta[e], bf16), bf16);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+epilogue16_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ residual, size_t n_vec, int act, int bf16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+    uint4 a = reinterpret_cast<uint4*>(y)[i];
+    uint32_t aw[4] = {a.x, a.y, a.z, a.w}, rw[4] = {0, 0, 0, 0};
+    if (residual) {
+      const uint4 r = reinterpret_cast<const uint4*>(residual)[i];
+      rw[0] = r.x; rw[1] = r.y; rw[2] = r.z; rw[3] = r.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint16_t lo = epilogue16(uint16_t(aw[j] & 0xffffu), act, residual != nullptr, uint16_t(rw[j] & 0xffffu), bf16 != 0);
+      const uint16_t hi = epilogue16(uint16_t(aw[j] >> 16), act, residual != nullptr, uint16_t(rw[j] >> 16), bf16 != 0);
+      aw[j] = uint32_t(lo) | (uint32_t(hi) << 16);
+    }
+    reinterpret_cast<uint4*>(y)[i] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+  }
+}
+
+template <typename K, typename... Args>
+int launch_pdl(K kern, dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = option(kOptNoPdl) ? 0 : 1;
+  ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, args...));
+  return ASRQ_OK;
+}
+
+}  // namespace
+
+int add_layernorm(const void* x, const void* delta, const void* gamma, const void* beta, float eps, void* x_out, void* h_out,
+                  int64_t rows, int64_t dim, int dtype, cudaStream_t stream) {
+  const int bf16 = dtype == ASRQ_BF16;
+  const dim3 grid(unsigned((rows + kLnWarps - 1) / kLnWarps)), block(32 * kLnWarps);
+  auto xp = static_cast<const uint16_t*>(x), dp = static_cast<const uint16_t*>(delta);
+  auto gp = static_cast<const uint16_t*>(gamma), bp = static_cast<const uint16_t*>(beta);
+  auto xo = static_cast<uint16_t*>(x_out), ho = static_cast<uint16_t*>(h_out);
+  const bool vec_ok = aligned16(x) && aligned16(h_out) && aligned16(gamma) && aligned16(beta) && (!delta || aligned16(delta)) &&
+                      (!x_out || aligned16(x_out));
+  if (vec_ok && dim == 1280) return launch_pdl(add_layernorm_kernel<5>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
+  if (vec_ok && dim == 1024) return launch_pdl(add_layernorm_kernel<4>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
+  if (vec_ok && dim == 2048) return launch_pdl(add_layernorm_kernel<8>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
+  if (vec_ok && dim == 256) return launch_pdl(add_layernorm_kernel<1>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
+  return launch_pdl(add_layernorm_kernel<0>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
+}
+
+// y = act(y) / y = residual + y over M x N 16-bit elements (M*N a multiple of 8, pointers 16-byte aligned)
+int epilogue16_apply(void* y, const void* residual, int64_t M, int64_t N, int act, int dtype, int sm_count, cudaStream_t stream) {
+  const size_t n_vec = size_t(M) * size_t(N) / 8;
+  const unsigned blocks = unsigned(std::max<size_t>(1, std::min<size_t>(size_t(sm_count) * 8, (n_vec + 255) / 256)));
+  return launch_pdl(epilogue16_kernel, dim3(blocks), dim3(256), stream, static_cast<uint16_t*>(y),
+                    static_cast<const uint16_t*>(residual), n_vec, act, int(dtype == ASRQ_BF16));
+}
+
+}  // namespace asrq

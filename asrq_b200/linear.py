@@ -62,6 +62,26 @@ class _on_device:
         return False
 
 
+def add_layernorm(x: torch.Tensor, delta, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5, write_sum: bool = True):
+    """``(x + delta, layer_norm(x + delta) * weight + bias)`` in one kernel (``delta`` may be None: then the
+    first result is ``x`` itself).  16-bit tensors on a CUDA device; the last dimension is normalised."""
+    dt = _require_cuda_16bit(x, "add_layernorm")
+    dim = x.shape[-1]
+    x2 = x.reshape(-1, dim)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    d2 = None
+    if delta is not None:
+        d2 = delta.reshape(-1, dim)
+        d2 = d2 if d2.is_contiguous() else d2.contiguous()
+    h = torch.empty_like(x2)
+    xo = torch.empty_like(x2) if (delta is not None and write_sum) else None
+    with _on_device(x.device):
+        _lib.call("asrq_add_layernorm", x2.data_ptr(), None if d2 is None else d2.data_ptr(), weight.data_ptr(),
+                  bias.data_ptr(), float(eps), None if xo is None else xo.data_ptr(), h.data_ptr(), x2.shape[0], dim, dt,
+                  torch.cuda.current_stream(x.device).cuda_stream)
+    return (x if xo is None else xo.reshape(x.shape)), h.reshape(x.shape)
+
+
 def _as_2d(x: torch.Tensor, k: int) -> torch.Tensor:
     if x.shape[-1] != k:
         raise ValueError(f"last dimension of the input is {x.shape[-1]}, expected in_features={k}")
@@ -141,6 +161,12 @@ class LinearQ(nn.Module):
             raise TypeError("LinearQ.bias must be float16 on the input's device")
 
     def forward(self, input):
+        return self.forward_fused(input)
+
+    def forward_fused(self, input, residual=None, gelu=False):
+        """``forward`` with the step that follows the layer in a transformer block done in the kernel's
+        epilogue: ``gelu(layer(input))`` or ``residual + layer(input)`` (``residual``: the output's shape and
+        dtype).  Same bits as the unfused module sequence."""
         # fp16 / bf16 only (the reference computes in whatever dtype the input has, asrq/core/linear.py:58-59;
         # an fp32 input raises here rather than silently running a slower path)
         dt = _require_cuda_16bit(input, "LinearQ.forward")
@@ -155,10 +181,23 @@ class LinearQ(nn.Module):
             return y.reshape(*input.shape[:-1], n)
         ws = _workspace(input.device, _lib.workspace_bytes(_lib.WS_LINEARQ, m, n, k))
         stream = torch.cuda.current_stream(input.device).cuda_stream
+        bias = None if self.bias is None else self.bias.data_ptr()
         with _on_device(input.device):
-            _lib.call("asrq_linearq_a16", self.bits, x2.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
-                      self.zeros.data_ptr(), None if self.bias is None else self.bias.data_ptr(), y.data_ptr(),
-                      m, n, k, self.group_size, dt, ws.data_ptr(), ws.numel(), stream)
+            if residual is None and not gelu:
+                _lib.call("asrq_linearq_a16", self.bits, x2.data_ptr(), self.weight.data_ptr(), self.scales.data_ptr(),
+                          self.zeros.data_ptr(), bias, y.data_ptr(), m, n, k, self.group_size, dt, ws.data_ptr(),
+                          ws.numel(), stream)
+            else:
+                r2 = None
+                if residual is not None:
+                    if residual.dtype != input.dtype or residual.numel() != m * n or residual.device != input.device:
+                        raise ValueError("forward_fused: residual must have the output's shape, dtype and device")
+                    r2 = residual.reshape(m, n)
+                    r2 = r2 if r2.is_contiguous() else r2.contiguous()
+                _lib.call("asrq_linearq_a16_fused", self.bits, x2.data_ptr(), self.weight.data_ptr(),
+                          self.scales.data_ptr(), self.zeros.data_ptr(), bias, None if r2 is None else r2.data_ptr(),
+                          y.data_ptr(), m, n, k, self.group_size, dt, _lib.ACT_GELU if gelu else _lib.ACT_NONE,
+                          ws.data_ptr(), ws.numel(), stream)
         if _CHECK:
             check_status(input.device)
         return y.reshape(*input.shape[:-1], n)

@@ -29,7 +29,7 @@ import torch.nn.functional as F
 
 from . import packing
 from .convert import linearq_from_linear
-from .linear import LinearQ
+from .linear import LinearQ, add_layernorm
 
 try:  # the model classes need transformers; the engine does not
     from transformers.models.whisper.modeling_whisper import (WhisperAttention, WhisperConfig, WhisperDecoder,
@@ -173,13 +173,32 @@ def _cat_linearq(parts: List[LinearQ]) -> LinearQ:
 
 
 class _Norm:
+    """Layer norm through the library's kernel (one launch; fp32 statistics, 16-bit in and out)."""
     __slots__ = ("w", "b", "eps")
 
     def __init__(self, w, b, eps=1e-5):
         self.w, self.b, self.eps = w, b, eps
 
     def __call__(self, x):
-        return F.layer_norm(x, (x.shape[-1],), self.w, self.b, self.eps)
+        return add_layernorm(x, None, self.w, self.b, self.eps)[1]
+
+
+def _fold_query_scale(lq: LinearQ, rows: int, s: float) -> bool:
+    """Folds the attention's query scaling (head_dim ** -0.5) into the first ``rows`` output rows of a layer:
+    (x W^T + b) * s == x (s W)^T + s b, with s W expressed by scaling the group scales and zeros.  Done only
+    when ``s`` is a power of two and every scaled scale and zero stays exactly representable (then the layer's
+    fp32 sums are scaled exactly); bias values whose product falls below the fp16 normal range are rounded
+    (absolute error <= 2^-25).  Returns whether the scaling was folded; otherwise the caller multiplies."""
+    if s <= 0 or math.frexp(s)[0] != 0.5:
+        return False
+    sc, ze = lq.scales[:rows].float() * s, lq.zeros[:rows].float() * s
+    if not (torch.equal(sc.half().float(), sc) and torch.equal(ze.half().float(), ze)):
+        return False
+    lq.scales[:rows] = sc.half()
+    lq.zeros[:rows] = ze.half()
+    if lq.bias is not None:
+        lq.bias[:rows] = (lq.bias[:rows].float() * s).half()
+    return True
 
 
 class WhisperEngine:
@@ -235,12 +254,11 @@ class WhisperEngine:
             a, c = L.self_attn, L.encoder_attn
             eng.dec_layers.append(dict(
                 ln1=norm(L.self_attn_layer_norm), qkv=_cat_linearq([lq(a.q_proj), lq(a.k_proj), lq(a.v_proj)]), out=lq(a.out_proj),
-                lnx=norm(L.encoder_attn_layer_norm), xq=lq(c.q_proj), xkv=_cat_linearq([lq(c.k_proj), lq(c.v_proj)]), xout=lq(c.out_proj),
+                lnx=norm(L.encoder_attn_layer_norm), xq=_cat_linearq([lq(c.q_proj)]), xkv=_cat_linearq([lq(c.k_proj), lq(c.v_proj)]), xout=lq(c.out_proj),
                 ln2=norm(L.final_layer_norm), fc1=lq(L.fc1), fc2=lq(L.fc2)))
         eng.dec_ln = norm(dec.layer_norm)
         eng.head = t(model.proj_out.weight)
-        if device.type == "cuda":
-            torch.cuda.current_stream(device).synchronize()  # fused weights complete before any launch reads them
+        eng._finalize()
         return eng
 
     @classmethod
@@ -294,9 +312,19 @@ class WhisperEngine:
                                        fc1=qlin(ffd, d), fc2=qlin(d, ffd)))
         eng.dec_ln = norm()
         eng.head = eng.embed
-        if device.type == "cuda":
-            torch.cuda.current_stream(device).synchronize()
+        eng._finalize()
         return eng
+
+    def _finalize(self):
+        """After the layers exist: fold the query scaling into the projections where that is exact."""
+        se, sd = (self.d // self.heads_e) ** -0.5, (self.d // self.heads_d) ** -0.5
+        for L in self.enc_layers:
+            L["q_folded"] = _fold_query_scale(L["qkv"], self.d, se)
+        for L in self.dec_layers:
+            L["q_folded"] = _fold_query_scale(L["qkv"], self.d, sd)
+            L["xq_folded"] = _fold_query_scale(L["xq"], self.d, sd)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()  # weights complete before any launch prefetches them
 
     def linear_layers(self) -> List[LinearQ]:
         out = []
@@ -328,10 +356,12 @@ class WhisperEngine:
         for L in self.enc_layers:
             h = L["ln1"](x)
             q, k, v = L["qkv"](h).split(self.d, dim=-1)
-            a = self._attend(q * scaling, self._split_heads(k, self.heads_e), self._split_heads(v, self.heads_e), self.heads_e)
-            x = x + L["out"](a)
+            if not L["q_folded"]:
+                q = q * scaling
+            a = self._attend(q, self._split_heads(k, self.heads_e), self._split_heads(v, self.heads_e), self.heads_e)
+            x = L["out"].forward_fused(a, residual=x)              # x + out_proj(a) in the kernel's epilogue
             h = L["ln2"](x)
-            x = x + L["fc2"](F.gelu(L["fc1"](h)))
+            x = L["fc2"].forward_fused(L["fc1"].forward_fused(h, gelu=True), residual=x)
             if clamp is not None:
                 x = torch.clamp(x, min=-clamp, max=clamp)
         return self.enc_ln(x)
@@ -343,8 +373,7 @@ class WhisperEngine:
             return
         dev, dt, nl = self.device, self.dtype, len(self.dec_layers)
         hd = self.d // self.heads_d
-        self.k_self = torch.zeros(nl, batch, self.heads_d, max_len, hd, device=dev, dtype=dt)
-        self.v_self = torch.zeros_like(self.k_self)
+        self.kv_self = torch.zeros(nl, 2, batch, self.heads_d, max_len, hd, device=dev, dtype=dt)  # keys, values
         self.k_cross = torch.empty(nl, batch, self.heads_d, src_len, hd, device=dev, dtype=dt)
         self.v_cross = torch.empty_like(self.k_cross)
         self.tok = torch.zeros(batch, dtype=torch.long, device=dev)      # token fed to the next step
@@ -377,16 +406,22 @@ class WhisperEngine:
         x = (self.embed[self.tok] + self.dec_pos[self.pos]).unsqueeze(1)  # (B, 1, d)
         for i, L in enumerate(self.dec_layers):
             h = L["ln1"](x)
-            q, k, v = L["qkv"](h).split(self.d, dim=-1)
-            self.k_self[i].index_copy_(2, self.pos, k.view(b, 1, self.heads_d, hd).transpose(1, 2))
-            self.v_self[i].index_copy_(2, self.pos, v.view(b, 1, self.heads_d, hd).transpose(1, 2))
-            a = self._attend(q * scaling, self.k_self[i], self.v_self[i], self.heads_d, self.mask)
-            x = x + L["out"](a)
+            qkv = L["qkv"](h)
+            q = qkv[..., :self.d]
+            if not L["q_folded"]:
+                q = q * scaling
+            # this position's key and value into the cache: one copy for both
+            self.kv_self[i].index_copy_(3, self.pos, qkv[..., self.d:].view(b, 1, 2, self.heads_d, hd).permute(2, 0, 3, 1, 4))
+            a = self._attend(q, self.kv_self[i, 0], self.kv_self[i, 1], self.heads_d, self.mask)
+            x = L["out"].forward_fused(a, residual=x)
             h = L["lnx"](x)
-            a = self._attend(L["xq"](h) * scaling, self.k_cross[i], self.v_cross[i], self.heads_d)
-            x = x + L["xout"](a)
+            q = L["xq"](h)
+            if not L["xq_folded"]:
+                q = q * scaling
+            a = self._attend(q, self.k_cross[i], self.v_cross[i], self.heads_d)
+            x = L["xout"].forward_fused(a, residual=x)
             h = L["ln2"](x)
-            x = x + L["fc2"](F.gelu(L["fc1"](h)))
+            x = L["fc2"].forward_fused(L["fc1"].forward_fused(h, gelu=True), residual=x)
         x = self.dec_ln(x).squeeze(1)
         torch.matmul(x, self.head.t(), out=self.logits)
         nxt = torch.argmax(self.logits, dim=-1)

@@ -136,6 +136,36 @@ int asrq_linearq_a16(int bits, const void* x, const uint8_t* w, const void* scal
                      size_t workspace_bytes, void* stream);
 
 /*
+ * The same layer with what follows it in a transformer block fused into the kernel's epilogue:
+ *   act = ASRQ_ACT_GELU   y = gelu(layer(x))            (exact erf form; Whisper's fc1)
+ *   residual != NULL      y = residual + layer(x)       (residual: M x N, the type of y; out_proj, fc2)
+ * Both act on the layer output ROUNDED to the 16-bit type, i.e. they give the bits of the unfused module
+ * sequence (LinearQ returns a 16-bit tensor; the activation or the add reads that and rounds again).
+ * The tcgen05 kernels (M > 16 on shapes they take) fuse the epilogue; on other paths the library runs
+ * one extra elementwise pass over y, so the call is valid for every shape asrq_linearq_a16 takes.
+ * y and residual 16-byte aligned, M*N a multiple of 8.  residual may alias y.
+ * The reference has no fused form: its model classes call LinearQ, then the activation / the add
+ * (asrq/models/transformers/whisper.py:100-125 through the stock encoder / decoder layer forward).
+ */
+#define ASRQ_ACT_NONE 0
+#define ASRQ_ACT_GELU 1
+int asrq_linearq_a16_fused(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros,
+                           const void* bias, const void* residual, void* y, int64_t M, int64_t N, int64_t K,
+                           int group_size, int dtype, int act, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/*
+ * x' = x + delta (delta may be NULL), h = LayerNorm(x') * gamma + beta over the last dimension.
+ * x, delta, x_out (optional; may alias x), h_out: rows x dim in the 16-bit type `dtype`; gamma, beta: dim
+ * values of that type.  Statistics in fp32 on the 16-bit-rounded x' (what "add, then layer_norm" computes).
+ * The pre-norm residual blocks of the decoder spend as many launches on these two steps as on the
+ * quantized layers; the reference leaves them to torch (nn.LayerNorm in its model classes,
+ * asrq/models/transformers/whisper.py:119,125).
+ */
+int asrq_add_layernorm(const void* x, const void* delta, const void* gamma, const void* beta, float eps, void* x_out,
+                       void* h_out, int64_t rows, int64_t dim, int dtype, void* stream);
+
+/*
  * W4A4 prologue: optional online Hadamard rotation over K (normalised
  * Walsh-Hadamard, butterflies with strides 1,2,4..K/2 then /sqrt(K), in fp32:
  * asrq/transforms/rotation/hadamard_utils.py:60-81) followed by per-token
