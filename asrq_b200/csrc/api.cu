@@ -361,16 +361,11 @@ static int linearq_a16(int bits, const void* x, const uint8_t* w, const void* sc
     int sms = 0;
     mid = current_device_sm_count(&sms) == ASRQ_OK && gemm_a16_skinny_supports(M, N, K, group_size, sms, workspace_bytes);
   }
-  // Large M (the persistent CTA-pair kernel): its four epilogue warps run under the next tile's main loop
-  // and have no slack for an erf per output or for a strided read of the residual (measured: a Whisper
-  // encoder pass went from 95 to 195 ms with both fused), so the epilogue is a pass of its own there.
-  const Epilogue in_kernel = M <= 256 ? ep : Epilogue();
   if (mid || (M > kGemvMaxM && tc_ok))
     rc = a16_gemm(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream,
-                  in_kernel, &fused);
+                  ep, &fused);
   else
     rc = a16_gemv(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes, stream);
-  if (M > 256) fused = false;
   if (rc || !want_ep || fused || M == 0) return rc;
   // the kernel that ran does not fuse the epilogue: one more pass over the output
   const DeviceFacts* f;

@@ -483,10 +483,12 @@ static int launch_tc(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmT
 bool gemm_a16_tc2_supports(int64_t M, int64_t N, int64_t K, int group_size);
 int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                  void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                 size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep);
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
-// `ep`: an epilogue the caller would like fused; *fused says whether the kernel that ran applied it (the
-// CTA-pair kernel does, the one-CTA kernel leaves it to the caller).
+// `ep`: an epilogue the caller would like fused; *fused says whether the kernel that ran applied it.  Neither
+// persistent kernel does: their four epilogue warps run under the next tile's main loop and have no slack for an
+// erf per output or a strided read of the residual (with both fused into the CTA-pair kernel a Whisper encoder
+// pass went from 95 to 195 ms, and the mere test for an epilogue per output cost the GEMM a quarter of its rate).
 int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                 void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
                 size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep, bool* fused) {
@@ -496,11 +498,10 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
   // stays here for the K split.  Option "tc_pair" = 1 / 0 forces / forbids it.
   const int pair_opt = option(kOptTcPair);
   const bool want_pair = pair_opt >= 0 ? pair_opt != 0 : M > 256;
-  if (want_pair && gemm_a16_tc2_supports(M, N, K, group_size)) {
-    *fused = true;
+  (void)ep;
+  if (want_pair && gemm_a16_tc2_supports(M, N, K, group_size))
     return gemm_a16_tc2(bits, x, w, scales, zeros, bias, y, M, N, K, group_size, dtype, workspace, workspace_bytes,
-                        sm_count, stream, ep);
-  }
+                        sm_count, stream);
   if (N % 128 || K % 64 || group_size <= 0 || group_size % 64 || K % group_size)
     return fail(ASRQ_ERR_SHAPE,
                 "w%da16 gemm: need N%%128==0, K%%64==0, group_size%%64==0, K%%group_size==0 "

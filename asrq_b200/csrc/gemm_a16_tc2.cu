@@ -33,8 +33,6 @@ struct GemmTc2Params {
   const __half* scales;
   const __half* zeros;
   const __half* bias;
-  const uint16_t* residual;  // fused epilogue: y = residual + layer output (NULL: none)
-  int act;                   // fused epilogue: activation on the layer output (kActNone / kActGelu)
   uint16_t* y;
   unsigned* status;
   int M, N, K, group_size, groups_per_row, bt, nstages, n_fpairs, n_ttiles;
@@ -50,6 +48,9 @@ constexpr int kT2MmaWarp = 1, kT2ProducerWarp = 9;
 // position of a warp among the twelve dequant warps (-1: not a dequant warp); scheduler 1 (warps 1, 5,
 // 9, 13, 17) hosts no ALU-heavy warp
 __constant__ int8_t kT2DequantPos[kT2Warps] = {0, -1, -1, -1, -1, -1, 1, 2, 3, -1, 4, 5, 6, -1, 7, 8, 9, -1, 10, 11};
+// drainers of the last unit's accumulator per lane quadrant (warp % 4): the epilogue warp (0) and two warps that
+// are idle by then (1, 2): dequant warps of the same quadrant, or the two warps without a role for quadrant 1
+__constant__ int8_t kT2DrainHelper[kT2Warps] = {-1, -1, 0, 0, 0, 0, 1, 1, 1, -1, 2, 2, 2, 1, -1, -1, -1, 2, -1, -1};
 constexpr int kT2MaxStages = 8;
 constexpr uint32_t kT2ATileBytes = 128 * 128;  // one dequantised A slot: 128 rows x 64 16-bit elements
 constexpr uint32_t kT2WSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
@@ -59,9 +60,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kT2Threads, 1)
 gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
                     const GemmTc2Params p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[3 * kT2MaxStages + 2 * kT2Slots + 4];
+  __shared__ __align__(8) uint64_t bars[3 * kT2MaxStages + 2 * kT2Slots + 5];
   __shared__ uint32_t tmem_slot;
 
+  // the next kernel on the stream may begin its set-up and weight fetch on SMs this grid leaves idle
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
@@ -82,6 +85,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   auto afree_bar = [&](int a) { return bar0 + 8u * (3 * kT2MaxStages + kT2Slots + a); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + b); };
   auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 2 + b); };
+  const uint32_t fin_bar = bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 4);  // the last unit's accumulator is complete
   // One arrival per warp on a barrier of CTA 0, from either CTA, after every lane has made its writes
   // visible to the async proxy (fence.proxy.async) and the warp has synchronised.
   // "Accumulator drained" carries no data through memory (the values are in registers), so its remote
@@ -118,6 +122,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
       tc::mbar_init(accf_bar(b), 1);
       tc::mbar_init(acce_bar(b), 8);  // four epilogue warps of each CTA
     }
+    tc::mbar_init(fin_bar, 1);
     tc::fence_barrier_init();
     tc::fence_proxy_async_smem();
     tc::prefetch_tmap(&tmx);
@@ -136,22 +141,81 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   const int nunits = p.n_fpairs * p.n_ttiles;  // a unit: feature tiles 2j, 2j+1 of token tile tt
   const int nkb = p.K / 64;
   const int dpos = kT2DequantPos[warp];
+  // The last unit of this pair: nothing runs under its epilogue, so the drain of its accumulator is shared
+  // by three warps per lane quadrant (the epilogue warp plus two warps that are idle by then) instead of one.
+  const int my_units = (nunits - cluster + nclusters - 1) / nclusters;
+  const int last_unit = cluster + (my_units - 1) * nclusters;
+  const int helper = kT2DrainHelper[warp];  // position among the three drainers of its quadrant, -1: none
+  // y = accumulator + bias for chunks ch0, ch0 + step, ... (32 tokens each) of `unit`'s tile, this warp's 32 features
+  auto drain = [&](int unit, uint32_t buf, int ch0, int step) {
+    const int qd = warp & 3;
+    const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
+    const int f = (2 * fp + int(rank)) * 128 + qd * 32 + lane;
+    const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
+    const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
+    const int rows_left = p.M - tt * p.bt;  // tokens of this tile that exist
+    for (int ch = ch0; ch < p.bt / 32; ch += step) {
+      // one output column (token) per register: the warp's 32 lanes write 32 consecutive features
+      uint16_t* yp = p.y + (size_t(tt) * p.bt + ch * 32) * p.N + f;
+      uint32_t r[32];
+      tc::tmem_ld_32x32(taddr + ch * 32, r);
+      tc::tmem_ld_wait();
+      if (rows_left >= (ch + 1) * 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+          yp += p.N;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (ch * 32 + j < rows_left) *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+          yp += p.N;
+        }
+      }
+    }
+  };
+  // a helper that is not an epilogue warp: wait for the last unit's accumulator, drain its share
+  auto help_drain = [&]() {
+    if (helper > 0 && tc::mbar_wait(fin_bar, 0u, p.status, 8)) {
+      tc::fence_after_sync();
+      drain(last_unit, uint32_t(my_units - 1) & 1u, helper, 3);
+    }
+  };
 
   if (warp == kT2ProducerWarp) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
+    // Launched with programmatic stream serialisation.  Packed weights are constants: the loads of the first
+    // ring of stages go out BEFORE griddepcontrol.wait, and the dequant warps unpack them into the A slots
+    // while the kernel before this one on the stream is still finishing; activations follow after the wait.
     if (lane == 0) {
       const uint32_t full0 = tc::mapa(full_bar(0), 0);  // CTA 0's full barriers, as seen from here
+      int pre = 0;
+      {
+        int s = 0;
+        for (int unit = cluster; unit < nunits && pre < nst; unit += nclusters) {
+          const int fp = unit % p.n_fpairs, row_w = (2 * fp + int(rank)) * 128;
+          for (int kb = 0; kb < nkb && pre < nst; ++kb, ++pre, ++s) {
+            const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
+            tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
+            tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
+          }
+        }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t ph = 0;
-      int s = 0;
+      int s = 0, step = 0;
       bool ok = true;
       for (int unit = cluster; unit < nunits && ok; unit += nclusters) {
         const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
         const int row_x = tt * p.bt + int(rank) * (p.bt / 2), row_w = (2 * fp + int(rank)) * 128;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb, ++step) {
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
           const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
-          tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
-          tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
+          if (step >= pre) {
+            tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
+            tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
+          }
           if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(s), 2u * xbytes);
           tc::tma_load_2d_pair(sb, &tmx, kb * 64, row_x, full0 + 8u * s);
           if (++s == nst) { s = 0; ph ^= 1u; }
@@ -189,7 +253,10 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
             // frees the stage and the A slot in both CTAs
             tc::mma_commit_pair(empty_bar(s), 3);
             tc::mma_commit_pair(afree_bar(a), 3);
-            if (kb + 1 == nkb) tc::mma_commit_pair(accf_bar(buf), 3);
+            if (kb + 1 == nkb) {
+              tc::mma_commit_pair(accf_bar(buf), 3);
+              if (unit == last_unit) tc::mma_commit_pair(fin_bar, 3);
+            }
           }
           if (++s == nst) { s = 0; ph ^= 1u; }
           if (++a == kT2Slots) { a = 0; dph ^= 1u; }
@@ -260,43 +327,25 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
       a += kT2Groups;
       if (a >= kT2Slots) { a -= kT2Slots; aph ^= 1u; }
     }
+    help_drain();
   } else if (warp >= 2 && warp <= 5) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
-    const int qd = warp & 3;
     uint32_t ucount = 0;
     bool ok = true;
     for (int unit = cluster; unit < nunits && ok; unit += nclusters, ++ucount) {
-      const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
       const uint32_t buf = ucount & 1u, aph = (ucount >> 1) & 1u;
-      const int f = (2 * fp + int(rank)) * 128 + qd * 32 + lane;
-      const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
       if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
       tc::fence_after_sync();
-      const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
-      // one output column (token) per register: the warp's 32 lanes write 32 consecutive features
-      uint16_t* yp = p.y + size_t(tt) * p.bt * p.N + f;
-      const int rows_left = p.M - tt * p.bt;  // tokens of this tile that exist
-      for (int ch = 0; ch < p.bt / 32; ++ch) {
-        uint32_t r[32];
-        tc::tmem_ld_32x32(taddr + ch * 32, r);
-        tc::tmem_ld_wait();
-        if (rows_left >= (ch + 1) * 32) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            *yp = finish16(__uint_as_float(r[j]) + bias, p.act, p.residual, size_t(yp - p.y), BF16);
-            yp += p.N;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (ch * 32 + j < rows_left) *yp = finish16(__uint_as_float(r[j]) + bias, p.act, p.residual, size_t(yp - p.y), BF16);
-            yp += p.N;
-          }
-        }
+      if (unit == last_unit) {
+        drain(unit, buf, 0, 3);  // shared with two helper warps of the same lane quadrant
+      } else {
+        drain(unit, buf, 0, 1);
       }
       tc::fence_before_sync();
       arrive_on_leader(acce_bar(buf), false);
     }
+  } else {
+    help_drain();  // warps without a role of their own (13, 17)
   }
 
   __syncwarp();
@@ -334,8 +383,17 @@ int launch_tc2(const CUtensorMap& tmx, const CUtensorMap& tmw, const GemmTc2Para
                cudaStream_t stream) {
   auto kern = gemm_a16_tc2_kernel<BITS, BF16>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem)) return rc;
-  kern<<<grid, kT2Threads, smem, stream>>>(tmx, tmw, p);  // cluster shape comes from __cluster_dims__
-  ASRQ_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};  // the cluster shape comes from __cluster_dims__
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kT2Threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = option(kOptNoPdl) ? 0 : 1;
+  ASRQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmx, tmw, p));
   return ASRQ_OK;
 }
 
@@ -348,7 +406,7 @@ bool gemm_a16_tc2_supports(int64_t M, int64_t N, int64_t K, int group_size) {
 
 int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, const void* zeros, const void* bias,
                  void* y, int64_t M, int64_t N, int64_t K, int group_size, int dtype, void* workspace,
-                 size_t workspace_bytes, int sm_count, cudaStream_t stream, const Epilogue& ep) {
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
   if (!gemm_a16_tc2_supports(M, N, K, group_size))
     return fail(ASRQ_ERR_SHAPE, "w%da16 gemm (pair): unsupported shape N=%lld K=%lld g=%d", bits, (long long)N,
                 (long long)K, group_size);
@@ -360,8 +418,6 @@ int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, 
   p.scales = static_cast<const __half*>(scales);
   p.zeros = static_cast<const __half*>(zeros);
   p.bias = static_cast<const __half*>(bias);
-  p.residual = static_cast<const uint16_t*>(ep.residual);
-  p.act = ep.act;
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
   p.M = int(M);
