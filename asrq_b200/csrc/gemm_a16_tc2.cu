@@ -9,11 +9,13 @@
 // what bounds the one-CTA kernel.
 //
 // Barriers (all in shared memory, same offsets in both CTAs):
-//   wfull[s]   local    packed weights of stage s landed (this CTA's own TMA)
+//   wfull[w]   local    packed weights of slot w landed (this CTA's own TMA; the weight ring is separate from the
+//                       activation stages, so weights run ahead of the MMAs by up to eight K blocks)
+//   wfree[w]   local    slot w unpacked by the four warps of a dequant group
 //   full[s]    CTA 0    both halves of the activation tile landed (TMA of both CTAs, byte count)
-//   empty[s]   both     stage s consumed: multicast tcgen05.commit of CTA 0's issuer
 //   deq[a]     CTA 0    A slot a written in BOTH CTAs (256 arrivals, CTA 1's come over the cluster)
-//   afree[a]   both     A slot a consumed (multicast commit)
+//   afree[a]   both     A slot a and activation stage a consumed (multicast tcgen05.commit of CTA 0's issuer; the
+//                       two rings have the same depth, so one commit per K block serves both)
 //   accf[b]    both     accumulator buffer b complete (multicast commit)
 //   acce[b]    CTA 0    buffer b drained by both CTAs' epilogues (256 arrivals)
 // Every barrier has one consumer that sees each phase in order.  No TMA multicast.  Every wait is bounded.
@@ -37,40 +39,81 @@ struct GemmTc2Params {
   unsigned* status;
   int M, N, K, group_size, groups_per_row, bt, nstages, n_fpairs, n_ttiles;
   int release_arrive;  // 1: the peer CTA's "A slot written" arrivals carry release semantics at cluster scope
+  long long* trace;    // builds with -DASRQ_TRACE: clock marks of one block (4 roles x 64 events x 4 marks), else NULL
+  int trace_block;
+  long long* gtrace;   // same builds: globaltimer marks of every block (entry, set-up, released, loads issued, exit)
 };
+
+#ifdef ASRQ_TRACE
+#define T2_MARK(role, idx, m)                                                                          \
+  do {                                                                                                 \
+    if (p.trace && int(blockIdx.x) == p.trace_block && lane == 0 && (idx) < 64)                        \
+      p.trace[((role) * 64 + (idx)) * 4 + (m)] = clock64();                                            \
+  } while (0)
+#else
+#define T2_MARK(role, idx, m) do { } while (0)
+#endif
 
 constexpr int kT2Groups = 3;
 constexpr int kT2Slots = 6;  // A slots: two per dequant group (slot = K-block count % 6, group = count % 3), so that a
                              // group need not wait for the MMAs of its previous block before starting the next
 constexpr int kT2Warps = 20;
 constexpr int kT2Threads = 32 * kT2Warps;
-constexpr int kT2MmaWarp = 1, kT2ProducerWarp = 9;
-// position of a warp among the twelve dequant warps (-1: not a dequant warp); scheduler 1 (warps 1, 5,
-// 9, 13, 17) hosts no ALU-heavy warp
-__constant__ int8_t kT2DequantPos[kT2Warps] = {0, -1, -1, -1, -1, -1, 1, 2, 3, -1, 4, 5, 6, -1, 7, 8, 9, -1, 10, 11};
-// drainers of the last unit's accumulator per lane quadrant (warp % 4): the epilogue warp (0) and two warps that
-// are idle by then (1, 2): dequant warps of the same quadrant, or the two warps without a role for quadrant 1
-__constant__ int8_t kT2DrainHelper[kT2Warps] = {-1, -1, 0, 0, 0, 0, 1, 1, 1, -1, 2, 2, 2, 1, -1, -1, -1, 2, -1, -1};
+// Roles by warp: 0 TMA producer of activations, 1 MMA issuer, 2 TMA producer of packed weights, 3 none, 4-15 dequant (group g = warps 4+4g .. 7+4g: one warp
+// on each of the SM's four schedulers, three dequant warps per scheduler), 16-19 epilogue (lane quadrant warp % 4).
+constexpr int kT2MmaWarp = 1, kT2ProducerWarp = 0, kT2WeightWarp = 2;
+constexpr int kT2FirstDequantWarp = 4, kT2FirstEpilogueWarp = 16;
+constexpr int kT2Drainers = 4;  // warps per lane quadrant that drain the last unit: the epilogue warp and one per group
 constexpr int kT2MaxStages = 8;
 constexpr uint32_t kT2ATileBytes = 128 * 128;  // one dequantised A slot: 128 rows x 64 16-bit elements
 constexpr uint32_t kT2WSlotBytes = 4096;       // packed weights of one K block (<= 128 x 32 B)
+constexpr int kT2WSlots = 8;                    // ring of packed-weight slots, independent of the activation stages
+
+// y = accumulator + bias for chunks ch0, ch0 + step, ... (32 tokens each) of one accumulator tile, for the calling
+// warp's 32 features (one per lane). Not inlined: it is called from three roles, and its 32 accumulator registers
+// must not add to the dequant warps' live set.
+template <bool BF16>
+__device__ __noinline__ void t2_drain(uint16_t* y, int N, int rows_left, int chunks, float bias, uint32_t taddr,
+                                      int ch0, int step) {
+  for (int ch = ch0; ch < chunks; ch += step) {
+    // one output column (token) per register: the warp's 32 lanes write 32 consecutive features
+    uint16_t* yp = y + size_t(ch) * 32 * N;
+    uint32_t r[32];
+    tc::tmem_ld_32x32(taddr + ch * 32, r);
+    tc::tmem_ld_wait();
+    if (rows_left >= (ch + 1) * 32) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+        yp += N;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (ch * 32 + j < rows_left) *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
+        yp += N;
+      }
+    }
+  }
+}
 
 template <int BITS, bool BF16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kT2Threads, 1)
 gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
                     const GemmTc2Params p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[3 * kT2MaxStages + 2 * kT2Slots + 5];
+  __shared__ __align__(8) uint64_t bars[2 * kT2MaxStages + 2 * kT2WSlots + 2 * kT2Slots + 5];
   __shared__ uint32_t tmem_slot;
 
   // the next kernel on the stream may begin its set-up and weight fetch on SMs this grid leaves idle
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef ASRQ_TRACE
+  if (p.gtrace && threadIdx.x == 0) p.gtrace[blockIdx.x * 8 + 0] = tc::globaltimer_ns();
+#endif
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t xbytes = uint32_t(p.bt / 2) * 128u;  // this CTA's half of the activation tile
   constexpr uint32_t a_ring_bytes = kT2Slots * kT2ATileBytes;
-  const uint32_t stage_bytes = xbytes + kT2WSlotBytes;
   constexpr uint32_t wbytes = 128u * 8u * BITS;
   const int nst = p.nstages;
 
@@ -79,13 +122,15 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   const int cluster = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
   const uint32_t bar0 = tc::smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (kT2MaxStages + s); };
+  constexpr int kB0 = 2 * kT2MaxStages + 2 * kT2WSlots;
   auto wfull_bar = [&](int s) { return bar0 + 8u * (2 * kT2MaxStages + s); };
-  auto deq_bar = [&](int a) { return bar0 + 8u * (3 * kT2MaxStages + a); };
-  auto afree_bar = [&](int a) { return bar0 + 8u * (3 * kT2MaxStages + kT2Slots + a); };
-  auto accf_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + b); };
-  auto acce_bar = [&](int b) { return bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 2 + b); };
-  const uint32_t fin_bar = bar0 + 8u * (3 * kT2MaxStages + 2 * kT2Slots + 4);  // the last unit's accumulator is complete
+  auto wfree_bar = [&](int s) { return bar0 + 8u * (2 * kT2MaxStages + kT2WSlots + s); };
+  auto deq_bar = [&](int a) { return bar0 + 8u * (kB0 + a); };
+  auto afree_bar = [&](int a) { return bar0 + 8u * (kB0 + kT2Slots + a); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (kB0 + 2 * kT2Slots + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (kB0 + 2 * kT2Slots + 2 + b); };
+  const uint32_t fin_bar = bar0 + 8u * (kB0 + 2 * kT2Slots + 4);  // the last unit's accumulator is complete
+  const uint32_t x_ring = a_ring_bytes, w_ring = a_ring_bytes + uint32_t(nst) * xbytes;  // offsets from base
   // One arrival per warp on a barrier of CTA 0, from either CTA, after every lane has made its writes
   // visible to the async proxy (fence.proxy.async) and the warp has synchronised.
   // "Accumulator drained" carries no data through memory (the values are in registers), so its remote
@@ -111,8 +156,10 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
       tc::mbar_init(full_bar(s), 1);
-      tc::mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < kT2WSlots; ++s) {
       tc::mbar_init(wfull_bar(s), 1);
+      tc::mbar_init(wfree_bar(s), 4);  // the four dequant warps of the group that unpacked the slot
     }
     for (int a = 0; a < kT2Slots; ++a) {
       tc::mbar_init(deq_bar(a), 8);  // four dequant warps of each CTA
@@ -137,129 +184,127 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   tc::cluster_sync();  // the peer's barriers are initialised before anything arrives on them
   tc::fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+#ifdef ASRQ_TRACE
+  if (p.gtrace && threadIdx.x == 0) p.gtrace[blockIdx.x * 8 + 1] = tc::globaltimer_ns();
+#endif
 
   const int nunits = p.n_fpairs * p.n_ttiles;  // a unit: feature tiles 2j, 2j+1 of token tile tt
   const int nkb = p.K / 64;
-  const int dpos = kT2DequantPos[warp];
+  // position among the twelve dequant warps, -1: not a dequant warp
+  const int dpos = (warp >= kT2FirstDequantWarp && warp < kT2FirstEpilogueWarp) ? warp - kT2FirstDequantWarp : -1;
   // The last unit of this pair: nothing runs under its epilogue, so the drain of its accumulator is shared
-  // by three warps per lane quadrant (the epilogue warp plus two warps that are idle by then) instead of one.
+  // by four warps per lane quadrant (the epilogue warp plus the dequant warps of that quadrant, idle by then).
   const int my_units = (nunits - cluster + nclusters - 1) / nclusters;
   const int last_unit = cluster + (my_units - 1) * nclusters;
-  const int helper = kT2DrainHelper[warp];  // position among the three drainers of its quadrant, -1: none
+  const int helper = dpos >= 0 ? 1 + (dpos >> 2) : (warp >= kT2FirstEpilogueWarp ? 0 : -1);  // position among the drainers
   // y = accumulator + bias for chunks ch0, ch0 + step, ... (32 tokens each) of `unit`'s tile, this warp's 32 features
   auto drain = [&](int unit, uint32_t buf, int ch0, int step) {
-    const int qd = warp & 3;
     const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
-    const int f = (2 * fp + int(rank)) * 128 + qd * 32 + lane;
-    const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
-    const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
-    const int rows_left = p.M - tt * p.bt;  // tokens of this tile that exist
-    for (int ch = ch0; ch < p.bt / 32; ch += step) {
-      // one output column (token) per register: the warp's 32 lanes write 32 consecutive features
-      uint16_t* yp = p.y + (size_t(tt) * p.bt + ch * 32) * p.N + f;
-      uint32_t r[32];
-      tc::tmem_ld_32x32(taddr + ch * 32, r);
-      tc::tmem_ld_wait();
-      if (rows_left >= (ch + 1) * 32) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
-          yp += p.N;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (ch * 32 + j < rows_left) *yp = float_to_out16(__uint_as_float(r[j]) + bias, BF16);
-          yp += p.N;
-        }
-      }
-    }
+    const int f = (2 * fp + int(rank)) * 128 + (warp & 3) * 32 + lane;
+    t2_drain<BF16>(p.y + size_t(tt) * p.bt * p.N + f, p.N, p.M - tt * p.bt, p.bt / 32,
+                   p.bias ? __half2float(__ldg(p.bias + f)) : 0.f,
+                   tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * 256u, ch0, step);
   };
   // a helper that is not an epilogue warp: wait for the last unit's accumulator, drain its share
   auto help_drain = [&]() {
     if (helper > 0 && tc::mbar_wait(fin_bar, 0u, p.status, 8)) {
       tc::fence_after_sync();
-      drain(last_unit, uint32_t(my_units - 1) & 1u, helper, 3);
+      drain(last_unit, uint32_t(my_units - 1) & 1u, helper, kT2Drainers);
     }
   };
 
   if (warp == kT2ProducerWarp) {
-    // ------------------------------ TMA producer (both CTAs) ------------------------------
-    // Launched with programmatic stream serialisation.  Packed weights are constants: the loads of the first
-    // ring of stages go out BEFORE griddepcontrol.wait, and the dequant warps unpack them into the A slots
-    // while the kernel before this one on the stream is still finishing; activations follow after the wait.
+    // ------------------------------ TMA producer of activations (both CTAs) ------------------------------
+    // Launched with programmatic stream serialisation: activations may be written by the kernel before this one
+    // on the stream, so their loads start after griddepcontrol.wait.
     if (lane == 0) {
       const uint32_t full0 = tc::mapa(full_bar(0), 0);  // CTA 0's full barriers, as seen from here
-      int pre = 0;
-      {
-        int s = 0;
-        for (int unit = cluster; unit < nunits && pre < nst; unit += nclusters) {
-          const int fp = unit % p.n_fpairs, row_w = (2 * fp + int(rank)) * 128;
-          for (int kb = 0; kb < nkb && pre < nst; ++kb, ++pre, ++s) {
-            const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
-            tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
-            tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
-          }
-        }
-      }
       asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef ASRQ_TRACE
+      if (p.gtrace) p.gtrace[blockIdx.x * 8 + 2] = tc::globaltimer_ns();
+#endif
       uint32_t ph = 0;
       int s = 0, step = 0;
+      (void)step;
       bool ok = true;
       for (int unit = cluster; unit < nunits && ok; unit += nclusters) {
-        const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
-        const int row_x = tt * p.bt + int(rank) * (p.bt / 2), row_w = (2 * fp + int(rank)) * 128;
+        const int tt = unit / p.n_fpairs;
+        const int row_x = tt * p.bt + int(rank) * (p.bt / 2);
         for (int kb = 0; kb < nkb; ++kb, ++step) {
-          if (!tc::mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
-          const uint32_t sb = base + a_ring_bytes + s * stage_bytes;
-          if (step >= pre) {
-            tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
-            tc::tma_load_2d(sb + xbytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
-          }
+          T2_MARK(3, step, 0);
+          if (!tc::mbar_wait(afree_bar(s), ph ^ 1u, p.status, 1)) { ok = false; break; }
+          T2_MARK(3, step, 1);
           if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(s), 2u * xbytes);
-          tc::tma_load_2d_pair(sb, &tmx, kb * 64, row_x, full0 + 8u * s);
+          tc::tma_load_2d_pair(base + x_ring + s * xbytes, &tmx, kb * 64, row_x, full0 + 8u * s);
           if (++s == nst) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == kT2WeightWarp) {
+    // ------------------------------ TMA producer of packed weights (both CTAs) ------------------------------
+    // Packed weights are constants, so this warp does not wait for the stream dependency: it runs up to
+    // kT2WSlots K blocks ahead of the dequant warps, which unpack the first blocks into the A slots while the
+    // kernel before this one on the stream is still finishing.  A slot is free again when the four warps of the
+    // dequant group that read it have arrived on wfree.
+    if (lane == 0) {
+      uint32_t ph = 0;
+      int s = 0, step = 0;
+      (void)step;
+      bool ok = true;
+      for (int unit = cluster; unit < nunits && ok; unit += nclusters) {
+        const int row_w = (2 * (unit % p.n_fpairs) + int(rank)) * 128;
+        for (int kb = 0; kb < nkb; ++kb, ++step) {
+          if (!tc::mbar_wait(wfree_bar(s), ph ^ 1u, p.status, 9)) { ok = false; break; }
+          tc::mbar_arrive_expect_tx(wfull_bar(s), wbytes);
+          tc::tma_load_2d(base + w_ring + s * kT2WSlotBytes, &tmw, kb * 8 * BITS, row_w, wfull_bar(s));
+          if (++s == kT2WSlots) { s = 0; ph ^= 1u; }
         }
       }
     }
   } else if (warp == kT2MmaWarp) {
     // ------------------------------ MMA issuer (CTA 0 only) ------------------------------
-    // run by the whole warp (counters and descriptors stay warp-uniform), tcgen05 instructions under an elected lane
+    // Run by the whole warp (counters and descriptors stay warp-uniform), tcgen05 instructions in one elected lane.
+    // The warp's own instruction latency is the critical path of the kernel (a barrier test costs 100 - 200 clocks,
+    // the MMAs of a K block run 512), so the tests for the NEXT block's two barriers are issued ahead of this
+    // block's MMAs and read after them; the waiting loop runs only when that probe found a barrier incomplete.
     if (rank == 0) {
-      const bool el = tc::elect_one();
+      const uint32_t el = tc::elect_one() ? 1u : 0u;
       const uint32_t idesc = tc::instr_desc(1u, BF16 ? 1u : 0u, 256u, uint32_t(p.bt));
-      uint32_t ph = 0, dph = 0, ucount = 0;
-      int s = 0, a = 0;
+      uint32_t dph = 0, ucount = 0, ready = 0;
+      int a = 0;  // A slot and activation stage of the current K block (the two rings have the same depth)
+      int tstep = 0;
+      (void)tstep;
       bool ok = true;
       for (int unit = cluster; unit < nunits && ok; unit += nclusters, ++ucount) {
         const uint32_t buf = ucount & 1u;
         const uint32_t d_tmem = tmem_base + buf * 256u;
         // the accumulator buffer must have been drained by both CTAs
         ok = tc::mbar_wait_spin(acce_bar(buf), ((ucount >> 1) & 1u) ^ 1u, p.status, 2);
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-          ok = (p.release_arrive ? tc::mbar_wait_spin_cluster(deq_bar(a), dph, p.status, 4)
-                                 : tc::mbar_wait_spin(deq_bar(a), dph, p.status, 4)) &&
-               tc::mbar_wait_spin(full_bar(s), ph, p.status, 3);
-          if (!ok) break;
-          tc::fence_after_sync();
-          // a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address field
-          const uint64_t da = tc::smem_desc_sw128(base + a * kT2ATileBytes);
-          const uint64_t db = tc::smem_desc_sw128(base + a_ring_bytes + s * stage_bytes);
-          if (el) {
-            tc::mma_f16_pair(d_tmem, da, db, idesc, uint32_t(kb != 0));
-            tc::mma_f16_pair(d_tmem, da + 2, db + 2, idesc, 1u);
-            tc::mma_f16_pair(d_tmem, da + 4, db + 4, idesc, 1u);
-            tc::mma_f16_pair(d_tmem, da + 6, db + 6, idesc, 1u);
-            // frees the stage and the A slot in both CTAs
-            tc::mma_commit_pair(empty_bar(s), 3);
-            tc::mma_commit_pair(afree_bar(a), 3);
-            if (kb + 1 == nkb) {
-              tc::mma_commit_pair(accf_bar(buf), 3);
-              if (unit == last_unit) tc::mma_commit_pair(fin_bar, 3);
-            }
+        for (int kb = 0; kb < nkb && ok; ++kb, ++tstep) {
+          T2_MARK(0, tstep, 0);
+          if (!ready || p.release_arrive) {
+            ok = (p.release_arrive ? tc::mbar_wait_spin_cluster(deq_bar(a), dph, p.status, 4)
+                                   : tc::mbar_wait_spin(deq_bar(a), dph, p.status, 4)) &&
+                 tc::mbar_wait_spin(full_bar(a), dph, p.status, 3);
+            if (!ok) break;
           }
-          if (++s == nst) { s = 0; ph ^= 1u; }
-          if (++a == kT2Slots) { a = 0; dph ^= 1u; }
+          T2_MARK(0, tstep, 2);
+          tc::fence_after_sync();
+          int an = a + 1;
+          uint32_t dphn = dph;
+          if (an == kT2Slots) { an = 0; dphn ^= 1u; }
+          // the four MMAs of the block (a K step of 16 elements = 32 bytes = +2 in the descriptors' 16-byte address
+          // field), one commit that frees the A slot and the activation stage in both CTAs, and the probe
+          ready = tc::mma4_commit_probe_pair(el, d_tmem, tc::smem_desc_sw128(base + a * kT2ATileBytes),
+                                             tc::smem_desc_sw128(base + x_ring + a * xbytes), idesc, uint32_t(kb != 0),
+                                             afree_bar(a), deq_bar(an), full_bar(an), dphn);
+          if (el && kb + 1 == nkb) {
+            tc::mma_commit_pair(accf_bar(buf), 3);
+            if (unit == last_unit) tc::mma_commit_pair(fin_bar, 3);
+          }
+          T2_MARK(0, tstep, 3);
+          a = an;
+          dph = dphn;
         }
       }
     }
@@ -269,18 +314,30 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
     const int dgroup = dpos >> 2;          // this warp group takes K blocks dgroup, dgroup+3, ... and owns A slot dgroup
     int unit = cluster, kb = dgroup;
     while (kb >= nkb && unit < nunits) { kb -= nkb; unit += nclusters; }
-    int s = dgroup % nst;
-    uint32_t ph = (dgroup / nst) & 1u;
+    int s = dgroup;  // packed-weight slot of the current K block (count % kT2WSlots) and the parity of its use count
+    uint32_t ph = 0;
+    static_assert(kT2Groups <= kT2WSlots, "the first block of every group starts in the ring's first pass");
     int a = dgroup;    // A slot of the current K block (count % kT2Slots) and the parity of its use count
     uint32_t aph = 0;
     const int kbpg = p.group_size / 64;  // K blocks per weight group
+    // Scale and zero of this thread's row for K block k of unit u, fetched one iteration (three K blocks) ahead.
+    // Volatile asm: the loads are issued here, not moved down to their first use.
+    int sz_unit = -1;
+    size_t sz_row = 0;
     auto load_sz = [&](int u, int k) -> uint32_t {
-      const int f = 2 * (u % p.n_fpairs) + int(rank);
+      if (u != sz_unit) {
+        sz_unit = u;
+        sz_row = (size_t(2 * (u % p.n_fpairs) + int(rank)) * 128 + t) * p.groups_per_row;
+      }
       const int gi = kbpg == 1 ? k : (kbpg == 2 ? (k >> 1) : k / kbpg);
-      const size_t idx = (size_t(f) * 128 + t) * p.groups_per_row + gi;
-      return uint32_t(__half_as_ushort(__ldg(p.scales + idx))) | (uint32_t(__half_as_ushort(__ldg(p.zeros + idx))) << 16);
+      uint16_t sv, zv;
+      asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(sv) : "l"(p.scales + sz_row + gi));
+      asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(zv) : "l"(p.zeros + sz_row + gi));
+      return uint32_t(sv) | (uint32_t(zv) << 16);
     };
     uint32_t sz_next = unit < nunits ? load_sz(unit, kb) : 0u;
+    int titer = 0;
+    (void)titer;
     while (unit < nunits) {
       const uint32_t sz = sz_next;
       int nunit = unit, nk = kb + kT2Groups;
@@ -295,16 +352,34 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         s2 = h2_as_u32(__half2half2(sh));
         z2 = h2_as_u32(__half2half2(zh));
       }
-      // the A slot must have been consumed by the MMAs of the K block that used it last (six blocks ago,
-      // this group's own): their commit arrived on the slot's barrier in both CTAs
-      if (!tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7) || !tc::mbar_wait(wfull_bar(s), ph, p.status, 5)) break;
-      const uint4* wp = reinterpret_cast<const uint4*>(smem + a_ring_bytes + s * stage_bytes + xbytes + t * (8 * BITS));
-      uint8_t* arow = smem + a * kT2ATileBytes + t * 128;
+      // the A slot must have been consumed by the MMAs of the K block that used it last (six blocks ago):
+      // their commit arrived on the slot's barrier in both CTAs.  Both barriers are tested in one go.
+      if (dpos == 0) T2_MARK(1, titer, 0);
+      {
+#if defined(ASRQ_T2_AB) && (ASRQ_T2_AB & 1)
+        const uint32_t got = 0;
+#else
+        const uint32_t got = tc::mbar_try_wait2(afree_bar(a), aph ^ 1u, wfull_bar(s), ph);
+#endif
+        if (!(got & 1u) && !tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7)) break;
+        if (!(got & 2u) && !tc::mbar_wait(wfull_bar(s), ph, p.status, 5)) break;
+      }
+      if (dpos == 0) T2_MARK(1, titer, 2);
       constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
+      uint4 qv[NV];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) qv[v] = tc::ld_shared_v4(base + w_ring + s * kT2WSlotBytes + t * (8 * BITS) + v * 16);
+      // The packed-weight slot is free once every lane holds its words.  A shared-memory load instruction returns all
+      // lanes' data together, so lane 0's arrival, made to depend on its own last word, comes after all of them.
+#if !(defined(ASRQ_T2_AB) && (ASRQ_T2_AB & 2))
+      if (lane == 0) tc::mbar_arrive_after(wfree_bar(s), qv[NV - 1].w);
+#endif
+      // 128-byte swizzle: 16-byte chunk c of row t lives at chunk position c ^ (t % 8); the row start is 128-byte
+      // aligned, so the position is an XOR on the address
+      const uint32_t arow = (base + a * kT2ATileBytes + t * 128) | uint32_t((t & 7) << 4);
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
-        const uint4 qv = wp[v];
-        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+        const uint32_t qw[4] = {qv[v].x, qv[v].y, qv[v].z, qv[v].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           constexpr int PW = 32 / BITS / 2;  // output pairs per word: 4 or 8
@@ -313,49 +388,69 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
 #pragma unroll
           for (int cc = 0; cc < PW / 4; ++cc) {
             const int chunk = (v * 4 + j) * (PW / 4) + cc;  // 16-byte chunk (8 elements) in the row
-            *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) =
-                make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
+            tc::st_shared_v4(arow ^ uint32_t(chunk << 4), o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
           }
         }
       }
       tc::fence_proxy_async_smem();
       arrive_on_leader(deq_bar(a), p.release_arrive != 0);
+#if defined(ASRQ_T2_AB) && (ASRQ_T2_AB & 2)
+      if (lane == 0) tc::mbar_arrive(wfree_bar(s));
+#endif
+      if (dpos == 0) T2_MARK(1, titer, 3);
+      ++titer;
       unit = nunit;
       kb = nk;
       s += kT2Groups;
-      if (s >= nst) { s -= nst; ph ^= 1u; }
+      if (s >= kT2WSlots) { s -= kT2WSlots; ph ^= 1u; }
       a += kT2Groups;
       if (a >= kT2Slots) { a -= kT2Slots; aph ^= 1u; }
     }
     help_drain();
-  } else if (warp >= 2 && warp <= 5) {
+  } else if (warp >= kT2FirstEpilogueWarp) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     uint32_t ucount = 0;
     bool ok = true;
     for (int unit = cluster; unit < nunits && ok; unit += nclusters, ++ucount) {
       const uint32_t buf = ucount & 1u, aph = (ucount >> 1) & 1u;
+      if (warp == kT2FirstEpilogueWarp) T2_MARK(2, ucount, 0);
       if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
+      if (warp == kT2FirstEpilogueWarp) T2_MARK(2, ucount, 1);
       tc::fence_after_sync();
       if (unit == last_unit) {
-        drain(unit, buf, 0, 3);  // shared with two helper warps of the same lane quadrant
+        drain(unit, buf, 0, kT2Drainers);  // shared with the dequant warps of the same lane quadrant
       } else {
         drain(unit, buf, 0, 1);
       }
       tc::fence_before_sync();
       arrive_on_leader(acce_bar(buf), false);
+      if (warp == kT2FirstEpilogueWarp) T2_MARK(2, ucount, 2);
     }
-  } else {
-    help_drain();  // warps without a role of their own (13, 17)
+#ifdef ASRQ_TRACE
+    if (p.gtrace && warp == kT2FirstEpilogueWarp && lane == 0) p.gtrace[blockIdx.x * 8 + 7] = tc::globaltimer_ns();
+#endif
   }
 
+#ifdef ASRQ_TRACE
+  if (p.gtrace && threadIdx.x == 0) p.gtrace[blockIdx.x * 8 + 3] = tc::globaltimer_ns();
+#endif
   __syncwarp();
   tc::fence_before_sync();
   __syncthreads();
+#ifdef ASRQ_TRACE
+  if (p.gtrace && threadIdx.x == 0) p.gtrace[blockIdx.x * 8 + 5] = tc::globaltimer_ns();
+#endif
   tc::cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its memory
+#ifdef ASRQ_TRACE
+  if (p.gtrace && threadIdx.x == 0) p.gtrace[blockIdx.x * 8 + 6] = tc::globaltimer_ns();
+#endif
   if (warp == kT2MmaWarp) {
     tc::fence_after_sync();
     tc::tmem_dealloc_pair(tmem_base, 512);
   }
+#ifdef ASRQ_TRACE
+  if (p.gtrace && threadIdx.x == 32 * kT2MmaWarp) p.gtrace[blockIdx.x * 8 + 4] = tc::globaltimer_ns();
+#endif
 }
 
 // Token-tile width: the multiple of 32 (<= 256, <= M) that minimises rounds over the CTA pairs x
@@ -369,7 +464,9 @@ int pick_bt(int64_t M, int64_t npairs, int nclusters) {
     if (bt > M && bt != 32) break;
     const int64_t units = npairs * ((M + bt - 1) / bt);
     const int64_t rounds = (units + nclusters - 1) / nclusters;
-    const double cost = double(rounds) * (bt + 24);
+    // a K block costs its MMAs (2 clocks per token column on a pair) or the fixed work beside them (dequantising a
+    // 128 x 64 weight tile, the issuing warp's own loop: about 540 clocks measured), whichever is longer
+    const double cost = double(rounds) * std::max(2.0 * bt, 540.0) + 1e-3 * double(units);
     if (cost <= best_cost) {
       best_cost = cost;
       best = bt;
@@ -427,13 +524,27 @@ int gemm_a16_tc2(int bits, const void* x, const uint8_t* w, const void* scales, 
   p.groups_per_row = int(K / group_size);
   p.n_fpairs = int(N / 256);
   p.release_arrive = option(kOptTcPairRelease);
+  p.trace = nullptr;
+  p.gtrace = nullptr;
+  p.trace_block = 0;
+#ifdef ASRQ_TRACE
+  if (option(kOptTrace) && workspace_bytes >= (8u << 20)) {
+    static unsigned launch_no = 0;  // consecutive launches alternate between two mark blocks
+    p.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + (4u << 20)) + size_t(launch_no & 1u) * 1024;
+    p.gtrace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + (5u << 20)) + size_t(launch_no & 7u) * 148 * 8;
+    ++launch_no;
+    p.trace_block = option(kOptTraceBlock);
+  }
+#endif
   const int max_clusters = sm_count / 2;
   p.bt = pick_bt(M, p.n_fpairs, max_clusters);
   p.n_ttiles = int((M + p.bt - 1) / p.bt);
-  const size_t stage_bytes = size_t(p.bt / 2) * 128 + kT2WSlotBytes;
-  const size_t budget = 227 * 1024 - 1024 - 512 - kT2Slots * kT2ATileBytes;
-  p.nstages = int(std::min<size_t>(kT2MaxStages, budget / stage_bytes));
-  const size_t smem = 1024 + kT2Slots * kT2ATileBytes + p.nstages * stage_bytes;
+  const size_t stage_bytes = size_t(p.bt / 2) * 128;  // one CTA's half of an activation tile
+  const size_t fixed = kT2Slots * kT2ATileBytes + kT2WSlots * kT2WSlotBytes;
+  const size_t budget = 227 * 1024 - 1024 - 512 - fixed;
+  p.nstages = kT2Slots;  // the activation ring is as deep as the A ring: one barrier frees both
+  if (size_t(p.nstages) * stage_bytes > budget) return fail(ASRQ_ERR_LIMIT, "w%da16 gemm (pair): shared memory", bits);
+  const size_t smem = 1024 + fixed + p.nstages * stage_bytes;
 
   const bool bf16 = dtype == ASRQ_BF16;
   CUtensorMap tmx, tmw;

@@ -41,6 +41,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
+// Two barriers tested by back-to-back try_waits whose results are read together: bit 0 = first, bit 1 = second.
+__device__ __forceinline__ uint32_t mbar_try_wait2(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b) {
+  uint32_t got;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .u32 x, y;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+      "selp.u32 x, 1, 0, p;\n\t"
+      "selp.u32 y, 2, 0, q;\n\t"
+      "or.b32 %0, x, y;\n\t}"
+      : "=r"(got)
+      : "r"(bar_a), "r"(parity_a), "r"(bar_b), "r"(parity_b)
+      : "memory");
+  return got;
+}
+// Arrival that is issued only after `dep` (a value the caller loaded) is available.
+__device__ __forceinline__ void mbar_arrive_after(uint32_t bar, uint32_t dep) {
+  asm volatile(
+      "{\n\t.reg .u32 z;\n\t"
+      "and.b32 z, %1, 0;\n\t"
+      "add.u32 z, z, %0;\n\t"
+      "mbarrier.arrive.shared::cta.b64 _, [z];\n\t}" ::"r"(bar),
+      "r"(dep)
+      : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 // Non-suspending poll, for the one thread whose wake-up latency is on the critical path.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
@@ -114,6 +147,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
       return false;
     }
   }
+}
+
+__device__ __forceinline__ long long globaltimer_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+  return t;
 }
 
 // ---- TMA -----------------------------------------------------------------------------
@@ -303,6 +342,44 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask)
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
       "h"(cta_mask)
       : "memory");
+}
+
+// One K block of a CTA pair's fp16/bf16 GEMM in a single instruction stream: tests of two barriers of the NEXT
+// block (parity `parity`), then - in the lane with el != 0 - four MMAs over consecutive 16-element K steps (the
+// descriptors advance by 32 bytes = 2 address units) and a commit to `commit_bar` in both CTAs.  The tests' results
+// are read after the MMAs have been issued, so their latency is not added to the issuing warp's critical path.
+// Returns 1 when both probed barriers had completed that phase.
+__device__ __forceinline__ uint32_t mma4_commit_probe_pair(uint32_t el, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                           uint32_t idesc, uint32_t accumulate, uint32_t commit_bar,
+                                                           uint32_t probe_a, uint32_t probe_b, uint32_t parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe, pacc, pt, p1, p2;\n\t"
+      ".reg .b64 a1, b1, a2, b2, a3, b3;\n\t"
+      ".reg .b16 m;\n\t"
+      "setp.ne.b32 pe, %1, 0;\n\t"
+      "setp.ne.b32 pacc, %6, 0;\n\t"
+      "setp.eq.b32 pt, %1, %1;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p1, [%8], %10;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p2, [%9], %10;\n\t"
+      "add.s64 a1, %3, 2;\n\tadd.s64 b1, %4, 2;\n\t"
+      "add.s64 a2, %3, 4;\n\tadd.s64 b2, %4, 4;\n\t"
+      "add.s64 a3, %3, 6;\n\tadd.s64 b3, %4, 6;\n\t"
+      "@pe tcgen05.mma.cta_group::2.kind::f16 [%2], %3, %4, %5, pacc;\n\t"
+      "@pe tcgen05.mma.cta_group::2.kind::f16 [%2], a1, b1, %5, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::2.kind::f16 [%2], a2, b2, %5, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::2.kind::f16 [%2], a3, b3, %5, pt;\n\t"
+      "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%7], m;\n\t"
+      "and.pred p1, p1, p2;\n\t"
+      "selp.u32 %0, 1, 0, p1;\n\t"
+      "}"
+      : "=r"(ready)
+      : "r"(el), "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(commit_bar), "r"(probe_a),
+        "r"(probe_b), "r"(parity)
+      : "memory");
+  return ready;
 }
 
 // ---- TMEM -> registers: lane = 32*(warp%4) + laneid, 32 consecutive 32-bit columns ------------
