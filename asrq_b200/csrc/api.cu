@@ -25,6 +25,9 @@ int gemm_a16_tc(int bits, const void* x, const uint8_t* w, const void* scales, c
 int add_layernorm(const void* x, const void* delta, const void* gamma, const void* beta, float eps, void* x_out, void* h_out,
                   int64_t rows, int64_t dim, int dtype, cudaStream_t stream);
 int epilogue16_apply(void* y, const void* residual, int64_t M, int64_t N, int act, int dtype, int sm_count, cudaStream_t stream);
+int add_rmsnorm(const void* x, const void* delta, const void* gamma, float eps, void* x_out, void* h_out, int64_t rows,
+                int64_t dim, int dtype, cudaStream_t stream);
+int silu_mul(const void* gu, void* out, int64_t rows, int64_t inter, int dtype, int sm_count, cudaStream_t stream);
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
                         int out_int8, cudaStream_t stream);
 int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void* bias, void* y, int64_t M, int64_t N,
@@ -401,6 +404,34 @@ int asrq_add_layernorm(const void* x, const void* delta, const void* gamma, cons
   if ((rc = device_facts(&f))) return rc;
   if (rows == 0) return ASRQ_OK;
   return add_layernorm(x, delta, gamma, beta, eps, x_out, h_out, rows, dim, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_add_rmsnorm(const void* x, const void* delta, const void* gamma, float eps, void* x_out, void* h_out, int64_t rows,
+                     int64_t dim, int dtype, void* stream) {
+  last_error().clear();
+  if (!x || !gamma || !h_out) return fail(ASRQ_ERR_NULL, "asrq_add_rmsnorm: x, gamma and h_out must not be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_add_rmsnorm: dtype %d", dtype);
+  if (rows < 0 || dim <= 0 || dim > (1 << 20) || rows > (int64_t(1) << 31) - 64)
+    return fail(ASRQ_ERR_SHAPE, "asrq_add_rmsnorm: rows=%lld dim=%lld", (long long)rows, (long long)dim);
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (rows == 0) return ASRQ_OK;
+  return add_rmsnorm(x, delta, gamma, eps, x_out, h_out, rows, dim, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, int dtype, void* stream) {
+  last_error().clear();
+  if (!gate_up || !out) return fail(ASRQ_ERR_NULL, "asrq_silu_mul: gate_up and out must not be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_silu_mul: dtype %d", dtype);
+  if (rows < 0 || inter <= 0 || inter % 8 != 0 || rows > (int64_t(1) << 31) - 64 || inter > (1 << 24))
+    return fail(ASRQ_ERR_SHAPE, "asrq_silu_mul: rows=%lld inter=%lld (a multiple of 8)", (long long)rows, (long long)inter);
+  if (!aligned16(gate_up) || !aligned16(out)) return fail(ASRQ_ERR_ALIGN, "asrq_silu_mul: gate_up and out must be 16-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (rows == 0) return ASRQ_OK;
+  return silu_mul(gate_up, out, rows, inter, dtype, f->sm_count, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,

@@ -3,10 +3,15 @@
 //   add_layernorm   x' = x + delta (optional), h = LayerNorm(x') * gamma + beta, one warp per row, fp32
 //                   statistics on the 16-bit-rounded x' (what the unfused sequence "add, then layer_norm"
 //                   computes), 16-bit in and out;
+//   add_rmsnorm     x' = x + delta (optional), h = (x' / rms(x')) rounded to 16 bits, then * gamma: the RMS norm of
+//                   the Qwen3 decoder blocks (statistics in fp32, the normalised value rounded before the weight
+//                   multiplies it, as the module does);
+//   silu_mul        out[m, i] = silu(gu[m, i]) * gu[m, I + i] on the output of a fused gate/up projection, each
+//                   factor rounded to 16 bits as the unfused sequence rounds them;
 //   epilogue16      y = act(y) or y = residual + y on an already written output: the fall-back for
-//                   layers whose kernel does not fuse the epilogue (the tcgen05 kernels fuse it).
+//                   layers whose kernel does not fuse the epilogue.
 //
-// Both open with griddepcontrol.launch_dependents / .wait and are launched with programmatic stream
+// All open with griddepcontrol.launch_dependents / .wait and are launched with programmatic stream
 // serialisation, so in a chain of this library's kernels (a decoder step replayed as a CUDA graph)
 // consecutive launches overlap their ramp-up with the predecessor's tail.
 #include <algorithm>
@@ -124,6 +129,115 @@ add_layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
   }
 }
 
+// One warp per row; VEC 16-byte vectors per lane when dim == 256 * VEC, else (VEC = 0) a strided loop.
+template <int VEC>
+__global__ void __launch_bounds__(32 * kLnWarps)
+add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ delta, const uint16_t* __restrict__ gamma,
+                   float eps, uint16_t* __restrict__ x_out, uint16_t* __restrict__ h_out, int rows, int dim, int bf16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kLnWarps + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t off = size_t(row) * dim;
+  if constexpr (VEC > 0) {
+    float v[VEC > 0 ? VEC * 8 : 1];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int e = (i * 32 + lane) * 8;
+      const uint4 a = *reinterpret_cast<const uint4*>(x + off + e);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      uint32_t dw[4] = {0, 0, 0, 0};
+      if (delta) {
+        const uint4 d = *reinterpret_cast<const uint4*>(delta + off + e);
+        dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w;
+      }
+      uint32_t ow[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo = in16(uint16_t(aw[j] & 0xffffu), bf16), hi = in16(uint16_t(aw[j] >> 16), bf16);
+        if (delta) {
+          lo += in16(uint16_t(dw[j] & 0xffffu), bf16);
+          hi += in16(uint16_t(dw[j] >> 16), bf16);
+        }
+        const uint16_t lo16 = float_to_out16(lo, bf16), hi16 = float_to_out16(hi, bf16);
+        ow[j] = uint32_t(lo16) | (uint32_t(hi16) << 16);
+        const float l = in16(lo16, bf16), h = in16(hi16, bf16);
+        v[i * 8 + 2 * j] = l;
+        v[i * 8 + 2 * j + 1] = h;
+        sq = fmaf(l, l, sq);
+        sq = fmaf(h, h, sq);
+      }
+      if (x_out) *reinterpret_cast<uint4*>(x_out + off + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rs = rsqrtf(sq / float(dim) + eps);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int e = (i * 32 + lane) * 8;
+      const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma + e));
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = in16(float_to_out16(v[i * 8 + 2 * j] * rs, bf16), bf16) * in16(uint16_t(gw[j] & 0xffffu), bf16);
+        const float hi = in16(float_to_out16(v[i * 8 + 2 * j + 1] * rs, bf16), bf16) * in16(uint16_t(gw[j] >> 16), bf16);
+        ow[j] = uint32_t(float_to_out16(lo, bf16)) | (uint32_t(float_to_out16(hi, bf16)) << 16);
+      }
+      *reinterpret_cast<uint4*>(h_out + off + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  } else {
+    float sq = 0.f;
+    for (int e = lane; e < dim; e += 32) {
+      float a = in16(x[off + e], bf16);
+      if (delta) a += in16(delta[off + e], bf16);
+      const uint16_t a16 = float_to_out16(a, bf16);
+      if (x_out) x_out[off + e] = a16;
+      const float c = in16(a16, bf16);
+      sq = fmaf(c, c, sq);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rs = rsqrtf(sq / float(dim) + eps);
+    for (int e = lane; e < dim; e += 32) {
+      float a = in16(x[off + e], bf16);
+      if (delta) a += in16(delta[off + e], bf16);
+      const float c = in16(float_to_out16(a, bf16), bf16);
+      h_out[off + e] = float_to_out16(in16(float_to_out16(c * rs, bf16), bf16) * in16(gamma[e], bf16), bf16);
+    }
+  }
+}
+
+// gu: rows x 2*inter (gate columns first, then up), out: rows x inter; eight elements per thread
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, int rows, int inter, int bf16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int vpr = inter / 8;  // vectors per output row
+  const size_t n_vec = size_t(rows) * vpr;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = i / vpr, c = (i - r * vpr) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * 2 * inter + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + r * 2 * inter + inter + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint16_t o2[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float gv = in16(uint16_t(gw[j] >> (16 * h)), bf16), uv = in16(uint16_t(uw[j] >> (16 * h)), bf16);
+        const float sv = in16(float_to_out16(gv / (1.f + expf(-gv)), bf16), bf16);  // silu, rounded as the module rounds it
+        o2[h] = float_to_out16(sv * uv, bf16);
+      }
+      ow[j] = uint32_t(o2[0]) | (uint32_t(o2[1]) << 16);
+    }
+    *reinterpret_cast<uint4*>(out + r * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
 __global__ void __launch_bounds__(256)
 epilogue16_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ residual, size_t n_vec, int act, int bf16) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -177,6 +291,27 @@ int add_layernorm(const void* x, const void* delta, const void* gamma, const voi
   if (vec_ok && dim == 2048) return launch_pdl(add_layernorm_kernel<8>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
   if (vec_ok && dim == 256) return launch_pdl(add_layernorm_kernel<1>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
   return launch_pdl(add_layernorm_kernel<0>, grid, block, stream, xp, dp, gp, bp, eps, xo, ho, int(rows), int(dim), bf16);
+}
+
+int add_rmsnorm(const void* x, const void* delta, const void* gamma, float eps, void* x_out, void* h_out, int64_t rows,
+                int64_t dim, int dtype, cudaStream_t stream) {
+  const int bf16 = dtype == ASRQ_BF16;
+  const dim3 grid(unsigned((rows + kLnWarps - 1) / kLnWarps)), block(32 * kLnWarps);
+  auto xp = static_cast<const uint16_t*>(x), dp = static_cast<const uint16_t*>(delta);
+  auto gp = static_cast<const uint16_t*>(gamma);
+  auto xo = static_cast<uint16_t*>(x_out), ho = static_cast<uint16_t*>(h_out);
+  const bool vec_ok = aligned16(x) && aligned16(h_out) && aligned16(gamma) && (!delta || aligned16(delta)) && (!x_out || aligned16(x_out));
+  if (vec_ok && dim == 2048) return launch_pdl(add_rmsnorm_kernel<8>, grid, block, stream, xp, dp, gp, eps, xo, ho, int(rows), int(dim), bf16);
+  if (vec_ok && dim == 1024) return launch_pdl(add_rmsnorm_kernel<4>, grid, block, stream, xp, dp, gp, eps, xo, ho, int(rows), int(dim), bf16);
+  if (vec_ok && dim == 256) return launch_pdl(add_rmsnorm_kernel<1>, grid, block, stream, xp, dp, gp, eps, xo, ho, int(rows), int(dim), bf16);
+  return launch_pdl(add_rmsnorm_kernel<0>, grid, block, stream, xp, dp, gp, eps, xo, ho, int(rows), int(dim), bf16);
+}
+
+int silu_mul(const void* gu, void* out, int64_t rows, int64_t inter, int dtype, int sm_count, cudaStream_t stream) {
+  const size_t n_vec = size_t(rows) * size_t(inter) / 8;
+  const unsigned blocks = unsigned(std::max<size_t>(1, std::min<size_t>(size_t(sm_count) * 8, (n_vec + 255) / 256)));
+  return launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), stream, static_cast<const uint16_t*>(gu), static_cast<uint16_t*>(out),
+                    int(rows), int(inter), int(dtype == ASRQ_BF16));
 }
 
 // y = act(y) / y = residual + y over M x N 16-bit elements (M*N a multiple of 8, pointers 16-byte aligned)

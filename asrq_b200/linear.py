@@ -82,6 +82,40 @@ def add_layernorm(x: torch.Tensor, delta, weight: torch.Tensor, bias: torch.Tens
     return (x if xo is None else xo.reshape(x.shape)), h.reshape(x.shape)
 
 
+def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float = 1e-6, write_sum: bool = True):
+    """``(x + delta, rms_norm(x + delta) * weight)`` in one kernel, with the rounding of the Qwen3 norm module (the
+    normalised value is rounded to the tensor's type before the weight multiplies it).  ``delta`` may be None."""
+    dt = _require_cuda_16bit(x, "add_rmsnorm")
+    dim = x.shape[-1]
+    x2 = x.reshape(-1, dim)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    d2 = None
+    if delta is not None:
+        d2 = delta.reshape(-1, dim)
+        d2 = d2 if d2.is_contiguous() else d2.contiguous()
+    h = torch.empty_like(x2)
+    xo = torch.empty_like(x2) if (delta is not None and write_sum) else None
+    with _on_device(x.device):
+        _lib.call("asrq_add_rmsnorm", x2.data_ptr(), None if d2 is None else d2.data_ptr(), weight.data_ptr(), float(eps),
+                  None if xo is None else xo.data_ptr(), h.data_ptr(), x2.shape[0], dim, dt,
+                  torch.cuda.current_stream(x.device).cuda_stream)
+    return (x if xo is None else xo.reshape(x.shape)), h.reshape(x.shape)
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for the output of a fused gate/up projection: ``gate_up`` is ``(..., 2 * I)`` with the
+    gate features first; returns ``(..., I)``."""
+    dt = _require_cuda_16bit(gate_up, "silu_mul")
+    inter = gate_up.shape[-1] // 2
+    g2 = gate_up.reshape(-1, 2 * inter)
+    g2 = g2 if g2.is_contiguous() else g2.contiguous()
+    out = torch.empty((g2.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+    with _on_device(gate_up.device):
+        _lib.call("asrq_silu_mul", g2.data_ptr(), out.data_ptr(), g2.shape[0], inter, dt,
+                  torch.cuda.current_stream(gate_up.device).cuda_stream)
+    return out.reshape(*gate_up.shape[:-1], inter)
+
+
 def _as_2d(x: torch.Tensor, k: int) -> torch.Tensor:
     if x.shape[-1] != k:
         raise ValueError(f"last dimension of the input is {x.shape[-1]}, expected in_features={k}")

@@ -166,6 +166,24 @@ int asrq_add_layernorm(const void* x, const void* delta, const void* gamma, cons
                        void* h_out, int64_t rows, int64_t dim, int dtype, void* stream);
 
 /*
+ * x' = x + delta (delta may be NULL), h = RMSNorm(x') * gamma over the last dimension, with the rounding of
+ * the Qwen3 decoder's norm module: x' / sqrt(mean(x'^2) + eps) in fp32, rounded to `dtype`, then multiplied by
+ * gamma and rounded again.  Same arguments as asrq_add_layernorm without beta.  The reference leaves the step
+ * to the stock module (Qwen3RMSNorm in asrq/models/nemo/canary_qwen.py:117-118,131-132).
+ */
+int asrq_add_rmsnorm(const void* x, const void* delta, const void* gamma, float eps, void* x_out, void* h_out,
+                     int64_t rows, int64_t dim, int dtype, void* stream);
+
+/*
+ * out[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i]: the gated activation between a fused gate/up
+ * projection (one LinearQ call over 2*inter output features) and the down projection
+ * (act_fn(gate_proj(x)) * up_proj(x) of Qwen3MLPQ, asrq/models/nemo/canary_qwen.py:70-86).  silu is rounded to
+ * `dtype` before the product, as the unfused sequence rounds it.  gate_up: rows x 2*inter, out: rows x inter,
+ * inter a multiple of 8, both 16-byte aligned.
+ */
+int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, int dtype, void* stream);
+
+/*
  * W4A4 prologue: optional online Hadamard rotation over K (normalised
  * Walsh-Hadamard, butterflies with strides 1,2,4..K/2 then /sqrt(K), in fp32:
  * asrq/transforms/rotation/hadamard_utils.py:60-81) followed by per-token

@@ -56,3 +56,45 @@ def test_fused_epilogues_match_the_unfused_sequence(m, k, n, dtype):
     assert bool(((y_act.float() - ref.float()).abs() <= tol).all())
     assert float((y_act != ref).float().mean()) < 0.02
     asrq_b200.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim,with_delta", [(64, 2048, True), (32, 2048, False), (7, 1024, True), (5, 256, True),
+                                                 (3, 96, True), (16, 128, False)])
+def test_add_rmsnorm(rows, dim, with_delta, dtype):
+    """Against the module sequence of the Qwen3 decoder block: residual add in the tensor's type, then the norm module
+    (fp32 statistics, the normalised value cast to the tensor's type, then times the weight).  The sum is bit-exact;
+    the normalised output may differ by one unit in the last place where the fp32 reduction order moves a rounding."""
+    gen = torch.Generator().manual_seed(rows * dim + 3)
+    x = torch.randn(rows, dim, generator=gen).to(dtype)
+    delta = (torch.randn(rows, dim, generator=gen) * 0.5).to(dtype) if with_delta else None
+    gamma = (1 + 0.1 * torch.randn(dim, generator=gen)).to(dtype)
+    eps = 1e-6
+    xd, dd, gd = x.to(DEV), None if delta is None else delta.to(DEV), gamma.to(DEV)
+    xs, h = asrq_b200.add_rmsnorm(xd, dd, gd, eps)
+    xs_ref = x if delta is None else (x + delta)
+    f = xs_ref.float()
+    n = (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).to(dtype)
+    h_ref = gamma * n
+    assert torch.equal(xs.cpu(), xs_ref)
+    ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+    err = (h.float().cpu() - h_ref.float()).abs()
+    assert bool((err <= 2 * ulp * h_ref.float().abs().clamp_min(2.0 ** -14)).all()), float(err.max())
+    assert float((err > 0).float().mean()) < 0.02
+    _, h2 = asrq_b200.add_rmsnorm(xd, dd, gd, eps, write_sum=False)
+    assert torch.equal(h2, h)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,inter", [(64, 6144), (1, 6144), (33, 512), (5, 8)])
+def test_silu_mul(rows, inter, dtype):
+    """act_fn(gate) * up with each factor rounded to the tensor's type, as the unfused module sequence rounds them."""
+    gen = torch.Generator().manual_seed(rows + inter)
+    gu = (torch.randn(rows, 2 * inter, generator=gen) * 2).to(dtype)
+    out = asrq_b200.silu_mul(gu.to(DEV))
+    ref = torch.nn.functional.silu(gu[:, :inter].float()).to(dtype) * gu[:, inter:]
+    err = (out.float().cpu() - ref.float()).abs()
+    ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+    assert bool((err <= 2 * ulp * ref.float().abs().clamp_min(2.0 ** -14)).all()), float(err.max())
+    assert float((err > 0).float().mean()) < 0.02   # expf against the library's exp: a last-place difference, rarely
+    assert out.shape == (rows, inter)
