@@ -59,6 +59,9 @@ SIGNATURES = {
     "asrq_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p, c_void_p, c_int64, c_int64, c_int,
                                  c_void_p]),
     "asrq_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "asrq_rtn_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                              c_void_p]),
+    "asrq_hadamard_fold": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p]),
     "asrq_hadamard_quant_int4": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
     "asrq_w4a4_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),

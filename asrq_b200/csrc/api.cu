@@ -28,6 +28,9 @@ int epilogue16_apply(void* y, const void* residual, int64_t M, int64_t N, int ac
 int add_rmsnorm(const void* x, const void* delta, const void* gamma, float eps, void* x_out, void* h_out, int64_t rows,
                 int64_t dim, int dtype, cudaStream_t stream);
 int silu_mul(const void* gu, void* out, int64_t rows, int64_t inter, int dtype, int sm_count, cudaStream_t stream);
+int rtn_pack(const void* w, int w_dtype, int bits, int group_size, int symmetric, int layout, uint8_t* weight, void* scales,
+             void* zeros, int64_t N, int64_t K, cudaStream_t stream);
+int hadamard_fold(const void* w, int w_dtype, float* out, int64_t N, int64_t K, cudaStream_t stream);
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
                         int out_int8, cudaStream_t stream);
 int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void* bias, void* y, int64_t M, int64_t N,
@@ -432,6 +435,36 @@ int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, i
   if ((rc = device_facts(&f))) return rc;
   if (rows == 0) return ASRQ_OK;
   return silu_mul(gate_up, out, rows, inter, dtype, f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_rtn_pack(const void* w, int w_dtype, int bits, int group_size, int symmetric, int layout, uint8_t* weight,
+                  void* scales, void* zeros, int64_t N, int64_t K, void* stream) {
+  last_error().clear();
+  if (!w || !weight || !scales || (layout == 0 && !zeros)) return fail(ASRQ_ERR_NULL, "asrq_rtn_pack: w, weight, scales (and zeros for layout 0) must not be NULL");
+  if (w_dtype != ASRQ_F16 && w_dtype != ASRQ_BF16 && w_dtype != ASRQ_F32) return fail(ASRQ_ERR_DTYPE, "asrq_rtn_pack: w_dtype %d", w_dtype);
+  if ((bits != 2 && bits != 4) || (layout != 0 && layout != 1) || (layout == 1 && (bits != 4 || !symmetric)))
+    return fail(ASRQ_ERR_SHAPE, "asrq_rtn_pack: bits=%d layout=%d symmetric=%d (layout 1 is signed 4-bit, symmetric)", bits, layout, symmetric);
+  if (N < 0 || K <= 0 || group_size < 8 || group_size % 8 != 0 || K % group_size != 0 || N > (int64_t(1) << 31) || K > (1 << 24))
+    return fail(ASRQ_ERR_SHAPE, "asrq_rtn_pack: N=%lld K=%lld group_size=%d (a multiple of 8 that divides K)", (long long)N, (long long)K, group_size);
+  if (reinterpret_cast<uintptr_t>(weight) % 4 != 0) return fail(ASRQ_ERR_ALIGN, "asrq_rtn_pack: weight must be 4-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (N == 0) return ASRQ_OK;
+  return rtn_pack(w, w_dtype, bits, group_size, symmetric != 0, layout, weight, scales, zeros, N, K, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_hadamard_fold(const void* w, int w_dtype, float* out, int64_t N, int64_t K, void* stream) {
+  last_error().clear();
+  if (!w || !out) return fail(ASRQ_ERR_NULL, "asrq_hadamard_fold: w and out must not be NULL");
+  if (w_dtype != ASRQ_F16 && w_dtype != ASRQ_BF16 && w_dtype != ASRQ_F32) return fail(ASRQ_ERR_DTYPE, "asrq_hadamard_fold: w_dtype %d", w_dtype);
+  if (N < 0 || K < 2 || K > 8192 || (K & (K - 1)) != 0 || N > (int64_t(1) << 31) - 1)
+    return fail(ASRQ_ERR_SHAPE, "asrq_hadamard_fold: N=%lld K=%lld (K a power of two, 2..8192)", (long long)N, (long long)K);
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (N == 0) return ASRQ_OK;
+  return hadamard_fold(w, w_dtype, out, N, K, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,

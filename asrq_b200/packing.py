@@ -146,3 +146,61 @@ def pack_w4a4(w: torch.Tensor, group_size: int = 128, hadamard: bool = True):
         wf = hadamard_pow2(wf)
     codes, scales, _ = rtn_quantize(wf, 4, group_size, True)
     return pack_signed_int4(codes), scales.to(torch.float16).contiguous()
+
+
+# --------------------------------------------------------------------------------------------------
+# the same steps as kernels (weights already on a CUDA device: no host round trip, no (N, K) temporaries)
+# --------------------------------------------------------------------------------------------------
+
+_W_DTYPES = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def _cuda_weight(w: torch.Tensor, who: str) -> int:
+    if not w.is_cuda:
+        raise RuntimeError(f"{who}: the weight is on {w.device}; this is the device version (use the host functions of this module otherwise)")
+    if w.ndim != 2 or w.dtype not in _W_DTYPES:
+        raise ValueError(f"{who}: a 2-D fp16, bf16 or fp32 weight is expected, got {tuple(w.shape)} {w.dtype}")
+    return _W_DTYPES[w.dtype]
+
+
+def rtn_pack_cuda(w: torch.Tensor, bits: int, group_size: int = 128, symmetric: bool = False):
+    """:func:`rtn_quantize` + :func:`pack_linearq` in one kernel: ``(weight uint8, scales fp16, zeros fp16)`` with the same
+    bits as the host path (every operation rounded to ``w.dtype``)."""
+    from . import _lib
+    dt = _cuda_weight(w, "rtn_pack_cuda")
+    n, k = w.shape
+    g = k if group_size == -1 else group_size
+    w = w.contiguous()
+    weight = torch.empty((n, k * bits // 8), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((n, k // g), dtype=torch.float16, device=w.device)
+    zeros = torch.empty((n, k // g), dtype=torch.float16, device=w.device)
+    with torch.cuda.device(w.device):
+        _lib.call("asrq_rtn_pack", w.data_ptr(), dt, bits, g, int(symmetric), 0, weight.data_ptr(), scales.data_ptr(),
+                  zeros.data_ptr(), n, k, torch.cuda.current_stream(w.device).cuda_stream)
+    return weight, scales, zeros
+
+
+def hadamard_fold_cuda(w: torch.Tensor) -> torch.Tensor:
+    """:func:`hadamard_pow2` of ``w.float()`` along the last dimension as a kernel (fp32 result, same bits)."""
+    from . import _lib
+    dt = _cuda_weight(w, "hadamard_fold_cuda")
+    w = w.contiguous()
+    out = torch.empty(w.shape, dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        _lib.call("asrq_hadamard_fold", w.data_ptr(), dt, out.data_ptr(), w.shape[0], w.shape[1],
+                  torch.cuda.current_stream(w.device).cuda_stream)
+    return out
+
+
+def pack_w4a4_cuda(w: torch.Tensor, group_size: int = 128, hadamard: bool = True):
+    """:func:`pack_w4a4` on the device: Hadamard fold (optional), then symmetric int4 codes as signed nibbles."""
+    from . import _lib
+    _cuda_weight(w, "pack_w4a4_cuda")
+    wf = hadamard_fold_cuda(w) if hadamard else w.float().contiguous()
+    n, k = wf.shape
+    weight = torch.empty((n, k // 2), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((n, k // group_size), dtype=torch.float16, device=w.device)
+    with torch.cuda.device(w.device):
+        _lib.call("asrq_rtn_pack", wf.data_ptr(), 2, 4, group_size, 1, 1, weight.data_ptr(), scales.data_ptr(), None, n, k,
+                  torch.cuda.current_stream(w.device).cuda_stream)
+    return weight, scales

@@ -46,6 +46,7 @@ extern "C" {
 
 #define ASRQ_F16 0
 #define ASRQ_BF16 1
+#define ASRQ_F32 2 /* accepted only where a function says so (the offline steps) */
 
 /* status codes (negative: rejected on the host, nothing was launched) */
 #define ASRQ_OK 0
@@ -182,6 +183,33 @@ int asrq_add_rmsnorm(const void* x, const void* delta, const void* gamma, float 
  * inter a multiple of 8, both 16-byte aligned.
  */
 int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, int dtype, void* stream);
+
+/*
+ * Offline step: round-to-nearest codes of a float weight on the reference's uniform grid, packed, on the device.
+ * Per (row, group of group_size inputs): asymmetric scale = (max - min) / (2^bits - 1), zero = min,
+ * code = clamp(round((w - zero) / scale), 0, 2^bits - 1); symmetric scale = max|w| / (2^(bits-1) - 1),
+ * code = clamp(round(w / scale), -(2^(bits-1) - 1), 2^(bits-1) - 1); round is half-to-even and every operation
+ * is rounded to the weight's own type w_dtype (ASRQ_F16, ASRQ_BF16 or ASRQ_F32), as the reference's tensor
+ * expressions round it (asrq/quantizers/base.py:61-77, asrq/quantizers/rtn.py:32-46).  The reference stops at
+ * fake-quantised floats; this also does the packing it lacks:
+ *   layout 0  LinearQ's buffers (asrq/core/linear.py:16-25,43-52): weight uint8 (N, K*bits/8), scales and zeros
+ *             fp16 (N, K/group_size); a symmetric grid is stored shifted (code + 2^(bits-1),
+ *             zero = -2^(bits-1) * scale) because LinearQ decodes unsigned codes;
+ *   layout 1  the W4A4 weight operand (asrq/matmulq/test.py:141-142): two's-complement nibbles (N, K/2), scales only;
+ *             bits must be 4 and the grid symmetric; zeros may be NULL.
+ * group_size a multiple of 8 that divides K; weight 4-byte aligned.
+ */
+int asrq_rtn_pack(const void* w, int w_dtype, int bits, int group_size, int symmetric, int layout, uint8_t* weight,
+                  void* scales, void* zeros, int64_t N, int64_t K, void* stream);
+
+/*
+ * Offline step: out = hadU(w) along K in fp32, the normalised Walsh-Hadamard transform in the butterfly order of
+ * matmul_hadU (asrq/transforms/rotation/hadamard_utils.py:64-81; strides 1, 2, ... K/2, then / sqrt(K)), K a power of
+ * two up to 8192.  It folds into a weight the rotation that asrq_hadamard_quant_* applies online to the
+ * activations (x . W^T == hadU(x) . hadU(W)^T), as the reference's offline fusion does for its rotations
+ * (asrq/transforms/rotation/utils.py:382-428).  w: N x K of w_dtype (ASRQ_F16, ASRQ_BF16 or ASRQ_F32), out: N x K fp32.
+ */
+int asrq_hadamard_fold(const void* w, int w_dtype, float* out, int64_t N, int64_t K, void* stream);
 
 /*
  * W4A4 prologue: optional online Hadamard rotation over K (normalised
