@@ -59,6 +59,7 @@ SIGNATURES = {
     "asrq_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p, c_void_p, c_int64, c_int64, c_int,
                                  c_void_p]),
     "asrq_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "asrq_dense_head": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "asrq_rtn_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                               c_void_p]),
     "asrq_hadamard_fold": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p]),
@@ -111,7 +112,12 @@ def check(fn_name: str, code: int) -> None:
         raise AsrqError(fn_name, code, last_error())
 
 
+CALLS = 0  # C-ABI calls made through call() in this process (benchmarks count a step's launches with it)
+
+
 def call(fn_name: str, *args) -> None:
+    global CALLS
+    CALLS += 1
     check(fn_name, getattr(load(), fn_name)(*args))
 
 

@@ -20,7 +20,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libasrq_b200.so")
 OBJ_DIR = os.path.join(PKG, "build")
 
-SOURCES = ["api.cu", "gemv_a16.cu", "gemv_a16_splitk.cu", "gemv_a16_staged.cu", "gemm_a16_tc.cu", "gemm_a16_tc2.cu", "gemm_a16_skinny.cu", "act_quant.cu", "glue.cu", "offline.cu", "w4a4_mma.cu", "w4a4_tc.cu"]
+SOURCES = ["api.cu", "gemv_a16.cu", "gemv_a16_splitk.cu", "gemv_a16_staged.cu", "gemm_a16_tc.cu", "gemm_a16_tc2.cu", "gemm_a16_skinny.cu", "act_quant.cu", "glue.cu", "offline.cu", "dense_head.cu", "w4a4_mma.cu", "w4a4_tc.cu"]
 HEADERS = ["common.cuh", "tcgen05.cuh", "dequant.cuh", os.path.join("..", "..", "include", "asrq_b200.h")]
 
 NVCC_FLAGS = [

@@ -31,6 +31,7 @@ int silu_mul(const void* gu, void* out, int64_t rows, int64_t inter, int dtype, 
 int rtn_pack(const void* w, int w_dtype, int bits, int group_size, int symmetric, int layout, uint8_t* weight, void* scales,
              void* zeros, int64_t N, int64_t K, cudaStream_t stream);
 int hadamard_fold(const void* w, int w_dtype, float* out, int64_t N, int64_t K, cudaStream_t stream);
+int dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, int sm_count, cudaStream_t stream);
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
                         int out_int8, cudaStream_t stream);
 int w4a4_linear_tc(const void* x, const uint8_t* qw, const void* sw, const void* bias, void* y, int64_t M, int64_t N,
@@ -435,6 +436,21 @@ int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, i
   if ((rc = device_facts(&f))) return rc;
   if (rows == 0) return ASRQ_OK;
   return silu_mul(gate_up, out, rows, inter, dtype, f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, void* stream) {
+  last_error().clear();
+  if (!x || !w || !y) return fail(ASRQ_ERR_NULL, "asrq_dense_head: x, w and y must not be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_dense_head: dtype %d", dtype);
+  if (M < 0 || M > 32 || N <= 0 || K <= 0 || K % 32 != 0 || K > 3200 || N > (int64_t(1) << 30))
+    return fail(ASRQ_ERR_SHAPE, "asrq_dense_head: M=%lld (at most 32) N=%lld K=%lld (a multiple of 32, at most 3200)", (long long)M,
+                (long long)N, (long long)K);
+  if (!aligned16(x) || !aligned16(w)) return fail(ASRQ_ERR_ALIGN, "asrq_dense_head: x and w must be 16-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (M == 0) return ASRQ_OK;
+  return dense_head(x, w, y, M, N, K, dtype, f->sm_count, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_rtn_pack(const void* w, int w_dtype, int bits, int group_size, int symmetric, int layout, uint8_t* weight,

@@ -116,6 +116,26 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out.reshape(*gate_up.shape[:-1], inter)
 
 
+def dense_head(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """``x @ weight.T`` for the floating-point output head of a decoding step (``weight`` is (vocabulary, K) in the
+    activations' 16-bit type): this library's kernel for up to 32 rows of ``x`` and K a multiple of 32 up to 3200,
+    ``torch.matmul`` otherwise."""
+    dt = _require_cuda_16bit(x, "dense_head")
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    m, n = x2.shape[0], weight.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    if m > 32 or k % 32 or k > 3200 or weight.dtype != x.dtype or not weight.is_contiguous():
+        torch.matmul(x2, weight.t(), out=out)
+        return out.reshape(*x.shape[:-1], n)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    with _on_device(x.device):
+        _lib.call("asrq_dense_head", x2.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, dt,
+                  torch.cuda.current_stream(x.device).cuda_stream)
+    return out.reshape(*x.shape[:-1], n)
+
+
 def _as_2d(x: torch.Tensor, k: int) -> torch.Tensor:
     if x.shape[-1] != k:
         raise ValueError(f"last dimension of the input is {x.shape[-1]}, expected in_features={k}")

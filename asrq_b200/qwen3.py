@@ -23,7 +23,7 @@ import torch.nn.functional as F
 
 from . import packing
 from .convert import linearq_from_linear
-from .linear import LinearQ, add_rmsnorm, silu_mul
+from .linear import LinearQ, add_rmsnorm, dense_head, silu_mul
 from .whisper import _cat_linearq
 
 try:
@@ -258,7 +258,7 @@ class Qwen3Engine:
         for i, L in enumerate(self.layers):
             x, delta = self._block(L, x, delta, cos, sin, self.kc[i], self.vc[i], 0, None, T, None)
         h = self._final(x, delta).view(B, T, H)[:, -1]
-        logits = h @ self.head.t()
+        logits = dense_head(h.contiguous(), self.head)
         self.pos = torch.full((1,), T, device=dev, dtype=torch.long)
         self.tok = logits.argmax(-1)
         self.last_logits = logits
@@ -277,7 +277,7 @@ class Qwen3Engine:
         for i, L in enumerate(self.layers):
             x, delta = self._block(L, x, delta, cos, sin, self.kc[i], self.vc[i], 0, self.pos, 1, mask)
         h = self._final(x, delta)
-        logits = h @ self.head.t()
+        logits = dense_head(h, self.head)
         self.last_logits.copy_(logits)
         self.tok.copy_(logits.argmax(-1))
         self.pos.add_(1)

@@ -29,7 +29,7 @@ import torch.nn.functional as F
 
 from . import packing
 from .convert import linearq_from_linear
-from .linear import LinearQ, add_layernorm
+from .linear import LinearQ, add_layernorm, dense_head
 
 try:  # the model classes need transformers; the engine does not
     from transformers.models.whisper.modeling_whisper import (WhisperAttention, WhisperConfig, WhisperDecoder,
@@ -423,7 +423,7 @@ class WhisperEngine:
             h = L["ln2"](x)
             x = L["fc2"].forward_fused(L["fc1"].forward_fused(h, gelu=True), residual=x)
         x = self.dec_ln(x).squeeze(1)
-        torch.matmul(x, self.head.t(), out=self.logits)
+        dense_head(x, self.head, out=self.logits)
         nxt = torch.argmax(self.logits, dim=-1)
         self.out_ids.index_copy_(0, self.pos, nxt.unsqueeze(0))
         self.tok.copy_(nxt)

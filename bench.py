@@ -668,14 +668,22 @@ class WhisperLargeV3(Workload):
         self.last_ids = self.engine.generate(self.xs[i % self.nsets], steps=self.STEPS)
 
     def count_launches(self):
-        """This library's kernel launches in one step: LinearQ calls of the encoder, of the cross-attention
-        key/value projections and of one decoder step times the number of tokens (a call with M <= 16 or
-        M > 32 tokens is one launch, 17..32 tokens two)."""
-        e = len(self.engine.enc_layers) * 4
-        x = len(self.engine.dec_layers)
-        per_call = 1 if self.batch <= 16 else (2 if self.batch <= 32 else 1)
-        d = len(self.engine.dec_layers) * 6 * per_call * self.STEPS
-        return e + x + d
+        """This library's kernel launches in one step, counted: the C-ABI calls of one eager (not graph-replayed) pass
+        through encoder, cross-attention key/value projections and one decoder token, the last times the number of
+        tokens.  A call is one launch, except that a large-M layer with a fused activation or residual runs that
+        step as a second kernel: those calls are counted twice."""
+        from asrq_b200 import _lib
+        eng, x = self.engine, self.xs[0]
+        c0 = _lib.CALLS
+        enc = eng.encode(x)
+        eng._alloc(self.batch, enc.shape[1], 4)
+        eng._cross_kv(enc)
+        c1 = _lib.CALLS
+        eng.decode(enc, 2, use_graph=False)
+        c2 = _lib.CALLS
+        torch.cuda.synchronize()
+        fused_large = len(eng.enc_layers) * 3 if self.batch * self.cfg.max_source_positions > 64 else 0  # out, fc1, fc2 of a layer
+        return (c1 - c0) + fused_large + (c2 - c1) // 2 * self.STEPS
 
     def phases(self):
         """Device time of the three phases of one step (CUDA events on the launching stream)."""
@@ -928,6 +936,9 @@ def measure(name, args, rank, local_rank, world, device, peaks, steps, warmup, f
     """One workload: parity check, K timed steps (max over ranks), per-kernel times, end-to-end leg, roofline,
     CPU baseline.  Returns the result object (the JSON line of the headline workload)."""
     from asrq_b200 import _lib, dp
+    if name == "c4" and (args.c4_layers or args.c4_tokens):
+        WhisperLargeV3.LAYERS = args.c4_layers or WhisperLargeV3.LAYERS
+        WhisperLargeV3.STEPS = args.c4_tokens or WhisperLargeV3.STEPS
     wl = WORKLOADS[name](device, args.seed + 1000 * rank)
     parity = bool(wl.check_parity())
     if not parity:
@@ -1016,6 +1027,9 @@ def measure(name, args, rank, local_rank, world, device, peaks, steps, warmup, f
                    "M": getattr(wl, "M", None), "K": getattr(wl, "K", None), "N": getattr(wl, "N", None)},
         "parity_checked": parity, "kernel_ms": kernel_ms, "gpu_launches": launches * steps * reps, "clocks": clocks,
     }
+    if name == "c4" and (args.c4_layers or args.c4_tokens):
+        line["config"]["reduced"] = (f"NOT the benchmark configuration: {wl.LAYERS}+{wl.LAYERS} layers, {wl.STEPS} tokens "
+                                     "(a bounded run for profiler captures)")
     if name == "c4":
         line["config"].update({"batch_per_gpu": wl.batch, "tokens": wl.STEPS, "layers": f"{wl.LAYERS}+{wl.LAYERS}",
                                "linearq_layers": wl.n_linear, "audio_seconds_per_step_per_gpu": wl.units_per_step()})
@@ -1069,6 +1083,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the other workloads (the `also` rows)")
     ap.add_argument("--no-group", action="store_true", help="one step per CUDA graph instead of a graph of consecutive steps")
+    ap.add_argument("--c4-layers", type=int, default=None,
+                    help="workload c4 at reduced depth (encoder and decoder layers each) and, with --c4-tokens, fewer tokens: "
+                         "for bounded profiler captures; the line's config says so and it is not the benchmark")
+    ap.add_argument("--c4-tokens", type=int, default=None)
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 5 if args.workload == "c4" else 200

@@ -185,6 +185,15 @@ int asrq_add_rmsnorm(const void* x, const void* delta, const void* gamma, float 
 int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, int dtype, void* stream);
 
 /*
+ * The floating-point output head of a decoding step: y[M, N] = x[M, K] . w[N, K]^T, all of the 16-bit type `dtype`,
+ * fp32 accumulation, for M <= 32 tokens and a vocabulary-sized N (any N >= 1).  The reference keeps these layers as
+ * nn.Linear (proj_out, asrq/models/transformers/whisper.py:268; lm_head, asrq/models/nemo/canary_qwen.py:179); after
+ * the 4-bit layers they are the largest read of a decoding step.  K a multiple of 32, at most 3200; x and w 16-byte
+ * aligned; w must not be written by work in flight on the stream (it is read ahead of the stream dependency).
+ */
+int asrq_dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, void* stream);
+
+/*
  * Offline step: round-to-nearest codes of a float weight on the reference's uniform grid, packed, on the device.
  * Per (row, group of group_size inputs): asymmetric scale = (max - min) / (2^bits - 1), zero = min,
  * code = clamp(round((w - zero) / scale), 0, 2^bits - 1); symmetric scale = max|w| / (2^(bits-1) - 1),

@@ -98,3 +98,29 @@ def test_silu_mul(rows, inter, dtype):
     assert bool((err <= 2 * ulp * ref.float().abs().clamp_min(2.0 ** -14)).all()), float(err.max())
     assert float((err > 0).float().mean()) < 0.02   # expf against the library's exp: a last-place difference, rarely
     assert out.shape == (rows, inter)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,k,n", [(32, 1280, 51866), (1, 1280, 51866), (20, 2048, 4099), (32, 2048, 16384), (7, 96, 50), (32, 3200, 1000)])
+def test_dense_head(m, k, n, dtype):
+    """The floating-point output head against fp32 on the same values (the reduction order differs from the library
+    GEMM's, so the comparison is against fp32): within 2e-3 of the row maximum, plus half a unit in the last place of
+    the value for bf16, whose rounding alone can cost 3.9e-3 of the row maximum."""
+    gen = torch.Generator().manual_seed(m + k + n)
+    x = torch.randn(m, k, generator=gen).to(dtype).to(DEV)
+    w = (torch.randn(n, k, generator=gen) * 0.05).to(dtype).to(DEV)
+    pad = torch.full((m * n + 64,), 7.0, dtype=dtype, device=DEV)
+    out = pad[:m * n].view(m, n)
+    y = asrq_b200.dense_head(x, w, out=out)
+    assert y.data_ptr() == out.data_ptr()
+    ref = x.float() @ w.float().t()
+    tol = 2e-3 * ref.abs().amax(dim=1, keepdim=True)
+    if dtype == torch.bfloat16:
+        tol = tol + 2.0 ** -8 * ref.abs()
+    assert bool(((y.float() - ref).abs() <= tol).all()), float((y.float() - ref).abs().max())
+    assert bool((pad[m * n:] == 7.0).all())                      # nothing written past the result
+    assert torch.equal(asrq_b200.dense_head(x, w), y)            # deterministic
+    # more than 32 rows go to the library GEMM
+    x2 = torch.randn(40, k, generator=gen).to(dtype).to(DEV)
+    assert asrq_b200.dense_head(x2, w).shape == (40, n)
+    asrq_b200.check_status()
