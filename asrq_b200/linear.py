@@ -32,13 +32,14 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 def check_status(device=None) -> None:
-    """Synchronises and raises if a kernel on the current stream reported a bounded wait that gave up."""
+    """Synchronises the device and raises if a kernel on any of its streams reported a bounded wait that gave up."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
-    ws = _workspaces.get(key)
-    if ws is not None:
-        with _on_device(device):
-            _lib.call("asrq_check_status", ws.data_ptr(), key[1])
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    torch.cuda.synchronize(idx)
+    for (dev, stream), ws in list(_workspaces.items()):
+        if dev == idx:
+            with _on_device(torch.device("cuda", idx)):
+                _lib.call("asrq_check_status", ws.data_ptr(), stream)
 
 
 class _on_device:
