@@ -31,6 +31,9 @@ int silu_mul(const void* gu, void* out, int64_t rows, int64_t inter, int dtype, 
 int rtn_pack(const void* w, int w_dtype, int bits, int group_size, int symmetric, int layout, uint8_t* weight, void* scales,
              void* zeros, int64_t N, int64_t K, cudaStream_t stream);
 int hadamard_fold(const void* w, int w_dtype, float* out, int64_t N, int64_t K, cudaStream_t stream);
+int qk_norm_rope(const void* qkv, const void* qw, const void* kw, const void* cos_t, const void* sin_t, const long long* pos_dev,
+                 long long pos_host, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int nq, int nkv, int hd,
+                 int64_t max_len, float eps, int dtype, cudaStream_t stream);
 int dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, int sm_count, cudaStream_t stream);
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
                         int out_int8, cudaStream_t stream);
@@ -436,6 +439,28 @@ int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, i
   if ((rc = device_facts(&f))) return rc;
   if (rows == 0) return ASRQ_OK;
   return silu_mul(gate_up, out, rows, inter, dtype, f->sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_qk_norm_rope(const void* qkv, const void* q_weight, const void* k_weight, const void* cos_table, const void* sin_table,
+                      const int64_t* pos_device, int64_t pos, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T,
+                      int n_q_heads, int n_kv_heads, int head_dim, int64_t max_len, float eps, int dtype, void* stream) {
+  last_error().clear();
+  if (!qkv || !q_weight || !k_weight || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
+    return fail(ASRQ_ERR_NULL, "asrq_qk_norm_rope: only pos_device may be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_qk_norm_rope: dtype %d", dtype);
+  if (B < 0 || T <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || (head_dim != 64 && head_dim != 128) || max_len <= 0 ||
+      (!pos_device && (pos < 0 || pos + T > max_len)) || B * T > (int64_t(1) << 30))
+    return fail(ASRQ_ERR_SHAPE, "asrq_qk_norm_rope: B=%lld T=%lld heads=%d/%d head_dim=%d (64 or 128) max_len=%lld pos=%lld", (long long)B,
+                (long long)T, n_q_heads, n_kv_heads, head_dim, (long long)max_len, (long long)pos);
+  if (reinterpret_cast<uintptr_t>(qkv) % 8 || reinterpret_cast<uintptr_t>(q_out) % 8 || reinterpret_cast<uintptr_t>(k_cache) % 8 ||
+      reinterpret_cast<uintptr_t>(v_cache) % 8)
+    return fail(ASRQ_ERR_ALIGN, "asrq_qk_norm_rope: qkv, q_out and the caches must be 8-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (B == 0) return ASRQ_OK;
+  return qk_norm_rope(qkv, q_weight, k_weight, cos_table, sin_table, reinterpret_cast<const long long*>(pos_device), (long long)pos, q_out,
+                      k_cache, v_cache, B, T, n_q_heads, n_kv_heads, head_dim, max_len, eps, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, void* stream) {

@@ -8,6 +8,10 @@
 //                   multiplies it, as the module does);
 //   silu_mul        out[m, i] = silu(gu[m, i]) * gu[m, I + i] on the output of a fused gate/up projection, each
 //                   factor rounded to 16 bits as the unfused sequence rounds them;
+//   qk_norm_rope    what sits between a fused q/k/v projection and the attention of a Qwen3 block, in one launch: the
+//                   per-head RMS norm of queries and keys, the rotary embedding, and the write of the new keys and
+//                   values into the caches at the sequence position (read from device memory when decoding under a
+//                   graph), every step rounded to 16 bits where the module sequence rounds it;
 //   epilogue16      y = act(y) or y = residual + y on an already written output: the fall-back for
 //                   layers whose kernel does not fuse the epilogue.
 //
@@ -238,6 +242,72 @@ silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, int
   }
 }
 
+// qkv: rows x (nq + 2 nkv) x hd, a row = sequence b, step t (rows = B * T).  One warp per (row, head); E = hd / 32
+// elements per lane; the rotary partner of element i is i +- hd / 2, i.e. the same slot of lane ^ 16.
+// q_out: B x nq x T x hd; caches: B x nkv x max_len x hd, written at position pos0 + t.
+template <int E>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(const uint16_t* __restrict__ qkv, const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
+                    const uint16_t* __restrict__ cos_t, const uint16_t* __restrict__ sin_t, const long long* __restrict__ pos_dev,
+                    long long pos_host, uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
+                    int rows, int T, int nq, int nkv, int max_len, float eps, int bf16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr int hd = 32 * E;
+  const int lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)rows * heads) return;
+  const int row = int(item / heads), head = int(item - (long long)row * heads);
+  const int b = row / T, t = row - b * T;
+  const long long pos = (pos_dev ? *pos_dev : pos_host) + t;
+  const uint16_t* src = qkv + (size_t(row) * heads + head) * hd + lane * E;
+  uint16_t v16[E];
+  if (E == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src);
+    v16[0] = uint16_t(u.x & 0xffffu); v16[1] = uint16_t(u.x >> 16); v16[2 % E] = uint16_t(u.y & 0xffffu); v16[3 % E] = uint16_t(u.y >> 16);
+  } else {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(src);
+    v16[0] = uint16_t(u & 0xffffu); v16[1] = uint16_t(u >> 16);
+  }
+  uint16_t* dst;
+  if (head < nq) {
+    dst = q_out + ((size_t(b) * nq + head) * T + t) * hd + lane * E;
+  } else if (head < nq + nkv) {
+    dst = k_cache + ((size_t(b) * nkv + (head - nq)) * max_len + size_t(pos)) * hd + lane * E;
+  } else {
+    dst = v_cache + ((size_t(b) * nkv + (head - nq - nkv)) * max_len + size_t(pos)) * hd + lane * E;
+  }
+  if (head < nq + nkv) {  // queries and keys: norm over the head, weight, rotary embedding
+    const uint16_t* w = (head < nq ? qw : kw) + lane * E;
+    float f[E], sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      f[i] = in16(v16[i], bf16);
+      sq = fmaf(f[i], f[i], sq);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rs = rsqrtf(sq / float(hd) + eps);
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float n = in16(float_to_out16(f[i] * rs, bf16), bf16);
+      const float y = in16(float_to_out16(in16(w[i], bf16) * n, bf16), bf16);
+      const float partner = __shfl_xor_sync(0xffffffffu, y, 16);
+      const float rot = lane < 16 ? -partner : partner;
+      const size_t ci = size_t(pos) * hd + lane * E + i;
+      const float a = in16(float_to_out16(y * in16(cos_t[ci], bf16), bf16), bf16);
+      const float c = in16(float_to_out16(rot * in16(sin_t[ci], bf16), bf16), bf16);
+      v16[i] = float_to_out16(a + c, bf16);
+    }
+  }
+  if (E == 4) {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(uint32_t(v16[0]) | (uint32_t(v16[1]) << 16), uint32_t(v16[2 % E]) | (uint32_t(v16[3 % E]) << 16));
+  } else {
+    *reinterpret_cast<uint32_t*>(dst) = uint32_t(v16[0]) | (uint32_t(v16[1]) << 16);
+  }
+}
+
 __global__ void __launch_bounds__(256)
 epilogue16_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ residual, size_t n_vec, int act, int bf16) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -312,6 +382,21 @@ int silu_mul(const void* gu, void* out, int64_t rows, int64_t inter, int dtype, 
   const unsigned blocks = unsigned(std::max<size_t>(1, std::min<size_t>(size_t(sm_count) * 8, (n_vec + 255) / 256)));
   return launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), stream, static_cast<const uint16_t*>(gu), static_cast<uint16_t*>(out),
                     int(rows), int(inter), int(dtype == ASRQ_BF16));
+}
+
+int qk_norm_rope(const void* qkv, const void* qw, const void* kw, const void* cos_t, const void* sin_t, const long long* pos_dev,
+                 long long pos_host, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int nq, int nkv, int hd,
+                 int64_t max_len, float eps, int dtype, cudaStream_t stream) {
+  const int64_t items = B * T * (nq + 2 * nkv);
+  const dim3 grid(unsigned((items + 7) / 8)), block(256);
+  auto p = [](const void* v) { return static_cast<const uint16_t*>(v); };
+  auto o = [](void* v) { return static_cast<uint16_t*>(v); };
+  const int bf16 = dtype == ASRQ_BF16;
+  if (hd == 128)
+    return launch_pdl(qk_norm_rope_kernel<4>, grid, block, stream, p(qkv), p(qw), p(kw), p(cos_t), p(sin_t), pos_dev, pos_host, o(q_out),
+                      o(k_cache), o(v_cache), int(B * T), int(T), nq, nkv, int(max_len), eps, bf16);
+  return launch_pdl(qk_norm_rope_kernel<2>, grid, block, stream, p(qkv), p(qw), p(kw), p(cos_t), p(sin_t), pos_dev, pos_host, o(q_out),
+                    o(k_cache), o(v_cache), int(B * T), int(T), nq, nkv, int(max_len), eps, bf16);
 }
 
 // y = act(y) / y = residual + y over M x N 16-bit elements (M*N a multiple of 8, pointers 16-byte aligned)

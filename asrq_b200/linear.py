@@ -117,6 +117,23 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out.reshape(*gate_up.shape[:-1], inter)
 
 
+def qk_norm_rope(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                 k_cache: torch.Tensor, v_cache: torch.Tensor, pos, B: int, T: int, n_q: int, n_kv: int, eps: float) -> torch.Tensor:
+    """Per-head RMS norm of queries and keys, rotary embedding, and the cache write for ``T`` new positions of ``B``
+    sequences, in one kernel.  ``qkv``: (B*T, (n_q + 2 n_kv) * head_dim) from a fused projection; ``cos``/``sin``:
+    (max_len, head_dim) tables; caches (B, n_kv, max_len, head_dim); ``pos``: first position, an int or a one-element int64
+    CUDA tensor (read on the device).  Returns the queries (B, n_q, T, head_dim)."""
+    dt = _require_cuda_16bit(qkv, "qk_norm_rope")
+    hd = k_cache.shape[-1]
+    q = torch.empty((B, n_q, T, hd), dtype=qkv.dtype, device=qkv.device)
+    on_dev = isinstance(pos, torch.Tensor)
+    with _on_device(qkv.device):
+        _lib.call("asrq_qk_norm_rope", qkv.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                  pos.data_ptr() if on_dev else None, 0 if on_dev else int(pos), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                  B, T, n_q, n_kv, hd, k_cache.shape[2], float(eps), dt, torch.cuda.current_stream(qkv.device).cuda_stream)
+    return q
+
+
 def dense_head(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """``x @ weight.T`` for the floating-point output head of a decoding step (``weight`` is (vocabulary, K) in the
     activations' 16-bit type): this library's kernel for up to 32 rows of ``x`` and K a multiple of 32 up to 3200,

@@ -23,7 +23,7 @@ import torch.nn.functional as F
 
 from . import packing
 from .convert import linearq_from_linear
-from .linear import LinearQ, add_rmsnorm, dense_head, silu_mul
+from .linear import LinearQ, add_rmsnorm, dense_head, qk_norm_rope, silu_mul
 from .whisper import _cat_linearq
 
 try:
@@ -212,25 +212,18 @@ class Qwen3Engine:
         return [L[k] for L in self.layers for k in ("qkv", "o", "gu", "down")]
 
     # ---- one block ------------------------------------------------------------------------------
-    def _block(self, L, x, delta, cos, sin, kc, vc, pos0: int, pos_t, T: int, mask):
+    def _block(self, L, x, delta, kc, vc, pos0: int, pos_t, T: int, mask):
         """x: (B*T, H) residual stream, delta: pending residual contribution or None.  Writes keys and values of the
         T new positions into the caches (at pos0.., or at the device-side position pos_t when decoding under a
         graph) and returns (x', delta') with delta' = the block's MLP output, still to be added."""
         B = x.shape[0] // T
         x, h = add_rmsnorm(x, delta, L["ln1"], self.eps)
-        qkv = L["qkv"](h).view(B, T, self.nq + 2 * self.nkv, self.hd)
-        q = _rms(qkv[:, :, :self.nq], L["qn"], self.eps).transpose(1, 2)
-        k = _rms(qkv[:, :, self.nq:self.nq + self.nkv], L["kn"], self.eps).transpose(1, 2)
-        v = qkv[:, :, self.nq + self.nkv:].transpose(1, 2)
-        q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+        # per-head q/k norms, rotary embedding and the cache write of the new positions: one kernel
+        q = qk_norm_rope(L["qkv"](h), L["qn"], L["kn"], self.cos, self.sin, kc, vc, pos0 if pos_t is None else pos_t, B, T,
+                         self.nq, self.nkv, self.eps)
         if pos_t is None:
-            kc[:, :, pos0:pos0 + T] = k
-            vc[:, :, pos0:pos0 + T] = v
             keys, vals = kc[:, :, :pos0 + T], vc[:, :, :pos0 + T]
-        else:  # one new position whose index lives on the device: scatter, attend over the whole cache under a mask
-            idx = pos_t.view(1, 1, 1, 1).expand(B, self.nkv, 1, self.hd)
-            kc.scatter_(2, idx, k)
-            vc.scatter_(2, idx, v)
+        else:  # one new position whose index lives on the device: attend over the whole cache under a mask
             keys, vals = kc, vc
         a = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask, is_causal=(mask is None and T > 1),
                                            enable_gqa=self.nq != self.nkv)
@@ -243,26 +236,38 @@ class Qwen3Engine:
         return add_rmsnorm(x, delta, self.norm, self.eps)[1]
 
     # ---- prefill / decode -------------------------------------------------------------------------
-    def prefill(self, inputs_embeds: torch.Tensor, max_new: int) -> torch.Tensor:
-        """inputs_embeds: (B, T, H).  Allocates caches for T + max_new positions, runs the prompt and returns the
-        first generated token ids (B,)."""
-        B, T, H = inputs_embeds.shape
-        self.B, self.T0, self.max_len = B, T, T + max_new
-        self._rotary_table(self.max_len)
+    def _alloc(self, B: int, max_len: int):
+        """Static state for a batch size and a maximal length; kept (with the captured graph) across calls."""
+        key = (B, max_len)
+        if getattr(self, "_alloc_key", None) == key:
+            return
         dev, dt = self.device, self.dtype
-        self.kc = [torch.zeros(B, self.nkv, self.max_len, self.hd, device=dev, dtype=dt) for _ in self.layers]
-        self.vc = [torch.zeros(B, self.nkv, self.max_len, self.hd, device=dev, dtype=dt) for _ in self.layers]
+        self.B, self.max_len = B, max_len
+        self._rotary_table(max_len)
+        self.kc = [torch.zeros(B, self.nkv, max_len, self.hd, device=dev, dtype=dt) for _ in self.layers]
+        self.vc = [torch.zeros(B, self.nkv, max_len, self.hd, device=dev, dtype=dt) for _ in self.layers]
+        self.pos = torch.zeros(1, device=dev, dtype=torch.long)
+        self.tok = torch.zeros(B, device=dev, dtype=torch.long)
+        self.last_logits = torch.zeros(B, self.head.shape[0], device=dev, dtype=dt)
+        self._alloc_key = key
+        self._graph = None
+
+    def prefill(self, inputs_embeds: torch.Tensor, max_new: int) -> torch.Tensor:
+        """inputs_embeds: (B, T, H).  Runs the prompt into caches sized for T + max_new positions and returns the first
+        generated token ids (B,)."""
+        B, T, H = inputs_embeds.shape
+        self._alloc(B, T + max_new)
+        self.T0 = T
+        dev, dt = self.device, self.dtype
         x = inputs_embeds.to(device=dev, dtype=dt).reshape(B * T, H).contiguous()
         delta = None
-        cos, sin = self.cos[:T], self.sin[:T]
         for i, L in enumerate(self.layers):
-            x, delta = self._block(L, x, delta, cos, sin, self.kc[i], self.vc[i], 0, None, T, None)
+            x, delta = self._block(L, x, delta, self.kc[i], self.vc[i], 0, None, T, None)
         h = self._final(x, delta).view(B, T, H)[:, -1]
         logits = dense_head(h.contiguous(), self.head)
-        self.pos = torch.full((1,), T, device=dev, dtype=torch.long)
-        self.tok = logits.argmax(-1)
-        self.last_logits = logits
-        self._graph = None
+        self.pos.fill_(T)
+        self.tok.copy_(logits.argmax(-1))
+        self.last_logits.copy_(logits)
         return self.tok.clone()
 
     def _step(self):
@@ -270,12 +275,10 @@ class Qwen3Engine:
         and advances self.pos."""
         B = self.B
         x = self.embed[self.tok]
-        cos = self.cos[self.pos].view(1, 1, 1, self.hd)
-        sin = self.sin[self.pos].view(1, 1, 1, self.hd)
         mask = (torch.arange(self.max_len, device=self.device) <= self.pos).view(1, 1, 1, self.max_len)
         delta = None
         for i, L in enumerate(self.layers):
-            x, delta = self._block(L, x, delta, cos, sin, self.kc[i], self.vc[i], 0, self.pos, 1, mask)
+            x, delta = self._block(L, x, delta, self.kc[i], self.vc[i], 0, self.pos, 1, mask)
         h = self._final(x, delta)
         logits = dense_head(h, self.head)
         self.last_logits.copy_(logits)

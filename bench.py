@@ -826,7 +826,218 @@ class WhisperLargeV3(Workload):
         return run, state, note, kind
 
 
-WORKLOADS = {"c1": W4A16Layer, "c2": W4A4Layer, "c3": DecodeSweep, "c4": WhisperLargeV3, "large": DecodeLargeLayer}
+def qwen3_1p7b_config(layers: int = 28, **over):
+    import transformers
+    cfg = dict(vocab_size=151936, hidden_size=2048, intermediate_size=6144, num_hidden_layers=layers, num_attention_heads=16,
+               num_key_value_heads=8, head_dim=128, max_position_embeddings=4096, rms_norm_eps=1e-6, tie_word_embeddings=True)
+    cfg.update(over)
+    return transformers.Qwen3Config(**cfg)
+
+
+class CanaryQwenShape(Workload):
+    """Canary-Qwen-2.5B-shaped model, random weights: a FastConformer-shaped stand-in encoder (32 blocks, d_model 1024,
+    FFN 4096, 8 heads, 8x subsampling; NeMo's encoder body is not available) whose linear layers are W4A4 with the online
+    Hadamard rotation, and a Qwen3-1.7B-shaped decoder (28 layers, hidden 2048, 16 query / 8 key-value heads, FFN 6144,
+    vocabulary 151936) W4A16 g128; a step transcribes 64 twenty-second windows (synthetic 80-bin log-mel N(0,1), 2000
+    frames -> 250 encoder tokens, 8 prompt tokens) with 200 greedy tokens each."""
+    name = "c5"
+    metric = "canary_qwen_shape_w4a4_w4a16_rtfx"
+    unit = "RTFx"
+    dtype = "f16 (fp32 / exact integer accumulation); encoder W4A4 g128, decoder W4 g128"
+    B, STEPS, FRAMES, MEL, ENC_LAYERS, DEC_LAYERS = 64, 200, 2000, 80, 32, 28
+    graph_steps = False
+    nsets = 2
+    kernels = ["encoder_linearqq"]
+
+    def __init__(self, device, seed, batch=None):
+        from asrq_b200 import conformer as C, qwen3 as Q
+        self.C, self.dev = C, device
+        self.batch = batch or self.B
+        enc = C.FastConformerStandIn(device, n_layers=self.ENC_LAYERS, seed=seed)
+        dec = Q.Qwen3Engine.random_init(qwen3_1p7b_config(self.DEC_LAYERS), device, seed=seed + 1)
+        self.model = C.SpeechLM(enc, dec, prompt_tokens=8, seed=seed)
+        gen = torch.Generator().manual_seed(seed + 1)
+        self.x_host = [torch.randn(self.batch, self.MEL, self.FRAMES, generator=gen).half().pin_memory() for _ in range(self.nsets)]
+        self.xs = [x.to(device) for x in self.x_host]
+        self.ids_host = torch.empty(self.batch, self.STEPS, dtype=torch.long).pin_memory()
+        self.n_linear = len(enc.linear_layers()) + len(dec.linear_layers())
+        self.l2_note = ("one step streams the packed weights of both models (about 1.3 GB with the fp16 head) per decoded token "
+                        "and GBs of activations: far beyond the 126 MiB L2; 2 alternating input batches")
+
+    def units_per_step(self):
+        return self.C.audio_seconds(self.batch, self.FRAMES)
+
+    def value_from(self, ms_per_step, world):
+        return self.units_per_step() * world / (ms_per_step * 1e-3)
+
+    def step(self, i):
+        self.last_ids = self.model.generate(self.xs[i % self.nsets], steps=self.STEPS)
+
+    def count_launches(self):
+        """C-ABI calls of one eager pass: encoder and prompt once, one decoded token times the number of tokens (a W4A4
+        layer is two calls: prologue and GEMM)."""
+        from asrq_b200 import _lib
+        m = self.model
+        c0 = _lib.CALLS
+        emb = m.prompt_embeddings(self.xs[0])
+        m.dec.prefill(emb, self.STEPS)
+        c1 = _lib.CALLS
+        m.dec.decode(2, use_graph=False)
+        c2 = _lib.CALLS
+        torch.cuda.synchronize()
+        return (c1 - c0) + (c2 - c1) // 2 * (self.STEPS - 1)
+
+    def phases(self):
+        m = self.model
+        torch.cuda.synchronize()
+        a = event()
+        enc = m.enc.encode(self.xs[0])
+        b = event()
+        emb = m.prompt_embeddings(self.xs[0])
+        m.dec.prefill(emb, self.STEPS)
+        c = event()
+        m.dec.decode(self.STEPS - 1)
+        d = event()
+        torch.cuda.synchronize()
+        e_ms = a.elapsed_time(b)
+        return {"encoder_ms": e_ms, "prompt_ms": b.elapsed_time(c) - e_ms, "decode_ms": c.elapsed_time(d),
+                "decode_ms_per_token": c.elapsed_time(d) / (self.STEPS - 1)}
+
+    def encoder_linear_times(self, reps=2):
+        """The W4A4 layer shapes of an encoder block at the encoder's token count (prologue + GEMM per call), each timed
+        alone with CUDA events, weight sets rotated over the blocks."""
+        enc = self.model.enc
+        m = self.batch * (self.FRAMES // 8)
+        out = {}
+        gen = torch.Generator(device=self.dev).manual_seed(0)
+        for key, k in (("ff1_a", 1024), ("ff1_b", 4096), ("q", 1024)):
+            x = torch.randn(m, k, device=self.dev, generator=gen).half()
+            layers = [L[key] for L in enc.layers]
+            for L in layers[:2]:
+                L(x)
+            torch.cuda.synchronize()
+            a = event()
+            for _ in range(reps):
+                for L in layers:
+                    L(x)
+            b = event()
+            torch.cuda.synchronize()
+            n = layers[0].out_features
+            ms = a.elapsed_time(b) / (reps * len(layers))
+            out[key] = {"M": m, "K": k, "N": n, "ms": ms, "tops": 2.0 * m * n * k / (ms * 1e-3) / 1e12}
+        return out
+
+    def check_parity(self):
+        """(1) every W4A4 call of the first encoder block on this batch's real activations, a row sample against the CPU
+        oracle (codes of the prologue recomputed on the CPU, exact integer sums, fp32 epilogue); (2) the decoder's first fused
+        q/k/v projection on the prompt's activations against the fp32 oracle; (3) the captured decoding graph against eager
+        stepping: identical tokens."""
+        from oracle import linearq_oracle as O
+        m = self.model
+        seen = {}
+
+        def hook(name, layer, inp, out):
+            if name not in seen:
+                seen[name] = (layer, inp.reshape(-1, inp.shape[-1]), out.reshape(-1, out.shape[-1]))
+        x = m.enc.subsample(self.xs[0][:4])
+        m.enc.block(m.enc.layers[0], x, m.enc._pos_emb(x.shape[1]), hook)
+        ok = True
+        for name, (layer, inp, out) in seen.items():
+            rows = torch.arange(0, inp.shape[0], max(1, inp.shape[0] // 48))
+            xi = inp[rows.to(self.dev)].cpu()
+            qa, sa, _ = O.hadamard_quant_int4(xi, True)
+            codes = O.unpack_signed_int4(layer.weight.cpu())
+            bias = None if layer.bias is None else layer.bias.cpu()
+            ref = O.w4a4_forward_fp32(qa, sa, codes, layer.scales.cpu(), bias, layer.group_size)
+            ok = ok and _rows_ok(out[rows.to(self.dev)], ref)
+        emb = m.prompt_embeddings(self.xs[0][:4])
+        from asrq_b200 import add_rmsnorm
+        L0 = m.dec.layers[0]
+        h = add_rmsnorm(emb.reshape(-1, emb.shape[-1]), None, L0["ln1"], m.dec.eps)[1]
+        y = L0["qkv"](h)
+        rows = torch.arange(0, h.shape[0], max(1, h.shape[0] // 64))
+        q = L0["qkv"]
+        ref = O.linearq_forward_fp32(h[rows.to(self.dev)].cpu(), q.weight.cpu(), q.scales.cpu(), q.zeros.cpu(), None, 4, 128)
+        ok = ok and _rows_ok(y[rows.to(self.dev)], ref)
+        a_ = m.dec.generate(emb, 5, use_graph=False).clone()
+        b_ = m.dec.generate(emb, 5, use_graph=True).clone()
+        return ok and torch.equal(a_, b_)
+
+    def e2e_step(self, i):
+        xh = self.x_host[i % self.nsets]
+        ids = self.model.generate(xh.to(self.dev, non_blocking=True), steps=self.STEPS)
+        self.ids_host.copy_(ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return xh.numel() * 2, self.ids_host.numel() * 8
+
+    e2e_api = ("asrq_b200.conformer.SpeechLM.generate(pinned host log-mel batch) -> token ids copied to pinned host memory, "
+               "synchronised every step")
+
+    def roofline(self, kernel_ms, peaks, int8_tops):
+        lin = self.encoder_linear_times()
+        ops = sum(2.0 * v["M"] * v["N"] * v["K"] for v in lin.values())
+        ms = sum(v["ms"] for v in lin.values())
+        ach = ops / (ms * 1e-3) / 1e12
+        peak = int8_tops or time_int8_peak(self.dev)
+        return {"kernel": "hadamard_quant + w4a4_tc_kernel on the encoder's W4A4 layer shapes, M = batch x 250 (prologue included)",
+                "bound": "tensor", "achieved": ach, "unit": "TOP/s", "peak": peak,
+                "peak_source": "torch._int_mm 8192^3 timed in this run", "frac": ach / peak if peak else None,
+                "traffic": None, "per_shape": lin}
+
+    # ---- CPU baseline: the quantized layers of one encoder block and one decoder layer on a bounded sample ----
+    @classmethod
+    def cpu_sample(cls, seed, case=None):
+        """The reference cannot express the W4A4 layers (its LinearQQ.forward returns None) and its encoder body is NeMo's,
+        so the CPU figure is a port restricted to the path: the nine W4A4 layers of one encoder block through the oracle
+        (Hadamard, int4 codes, integer sums) on 2 utterances, and the four fused W4A16 layer shapes of one decoder layer
+        through the reference's LinearQ.forward (oracle/_ref when staged, else the port) on the batch of 64 for one token
+        and on 2 utterances' prompts; everything else of the models (attention, convolutions, norms, the head) is left out,
+        i.e. the figure is an upper bound of the CPU's RTFx."""
+        from oracle import linearq_oracle as O
+        gen = torch.Generator().manual_seed(seed)
+        enc_u, T, H = 2, cls.FRAMES // 8, 2048
+        enc_layers = []
+        for n, k in ((4096, 1024), (1024, 4096), (1024, 1024), (1024, 1024), (1024, 1024), (1024, 1024), (1024, 1024), (4096, 1024), (1024, 4096)):
+            codes = torch.randint(-7, 8, (n, k), generator=gen, dtype=torch.int8)
+            sw = (torch.rand(n, k // 128, generator=gen) * 0.005 + 0.001).half()
+            enc_layers.append((codes, sw, torch.randn(enc_u * T, k, generator=gen).half()))
+        dec_layers = []
+        for n, k in ((4096, 2048), (2048, 2048), (12288, 2048), (2048, 6144)):
+            c = O.make_c3(seed=seed + n, m=1, k=k, n=n, bits=4, group_size=128)
+            ref = _reference_linearq(c, None)
+            dec_layers.append((c, ref, torch.randn(cls.B, k, generator=gen).half(), torch.randn(enc_u * (T + 8), k, generator=gen).half()))
+        state = {}
+        kind = "reference (decoder layers) + port (encoder layers)" if dec_layers[0][1] is not None else "port"
+
+        def fwd(c, ref, x):
+            if ref is not None:
+                return ref.forward(x)
+            return O.linearq_forward(x, c["weight"], c["scales"], c["zeros"], None, 4, 128)
+
+        def run():
+            with torch.no_grad():
+                t0 = time.perf_counter()
+                for codes, sw, x in enc_layers:
+                    qa, sa, _ = O.hadamard_quant_int4(x, True)
+                    O.w4a4_forward_fp32(qa, sa, codes, sw, None, 128)
+                t1 = time.perf_counter()
+                for c, ref, xt, xp in dec_layers:
+                    fwd(c, ref, xt)
+                t2 = time.perf_counter()
+                for c, ref, xt, xp in dec_layers:
+                    fwd(c, ref, xp)
+                t3 = time.perf_counter()
+            state["enc_block_per_utterance_s"] = (t1 - t0) / enc_u
+            state["dec_layer_token_s"] = t2 - t1
+            state["dec_layer_prompt_per_utterance_s"] = (t3 - t2) / enc_u
+        note = (f"quantized layers only: the 9 W4A4 layers of 1 encoder block on {enc_u} utterances (oracle port), the 4 fused W4A16 "
+                f"layers of 1 decoder layer on the batch of {cls.B} for 1 token and on {enc_u} prompts (reference LinearQ.forward "
+                "where staged); extrapolated linearly to 32 blocks x 64 utterances + 28 layers x (64 prompts + 200 tokens); "
+                "attention, convolutions, norms and the head are left out (the figure is an upper bound of the CPU's RTFx)")
+        return run, state, note, kind
+
+
+WORKLOADS = {"c1": W4A16Layer, "c2": W4A4Layer, "c3": DecodeSweep, "c4": WhisperLargeV3, "c5": CanaryQwenShape, "large": DecodeLargeLayer}
 
 
 def library_gemm_same_shape(device, m, k, n, kind, reps=40):
@@ -898,6 +1109,11 @@ def run_cpu(cls, seed, budget_s, max_runs, min_runs=1, case=None):
                 + 32 * 128 * units["dec_layer_token_s"])                      # seconds per batch of 32 utterances
         out["value"] = 32 * 30.0 / wall
         out["extrapolated"] = dict(units, seconds_per_batch_of_32=wall)
+    elif cls.name == "c5":
+        wall = (cls.ENC_LAYERS * cls.B * units["enc_block_per_utterance_s"]
+                + cls.DEC_LAYERS * (cls.B * units["dec_layer_prompt_per_utterance_s"] + cls.STEPS * units["dec_layer_token_s"]))
+        out["value"] = cls.B * cls.FRAMES / 100.0 / wall
+        out["extrapolated"] = dict(units, seconds_per_batch_of_64=wall)
     else:
         scale = 1e12 if cls.unit in ("TOP/s", "TFLOP/s") else 1e9
         out["value"] = units / dt / scale
@@ -1030,12 +1246,17 @@ def measure(name, args, rank, local_rank, world, device, peaks, steps, warmup, f
     if name == "c4" and (args.c4_layers or args.c4_tokens):
         line["config"]["reduced"] = (f"NOT the benchmark configuration: {wl.LAYERS}+{wl.LAYERS} layers, {wl.STEPS} tokens "
                                      "(a bounded run for profiler captures)")
+    if name == "c5":
+        line["config"].update({"batch_per_gpu": wl.batch, "tokens": wl.STEPS, "layers": f"{wl.ENC_LAYERS} blocks + {wl.DEC_LAYERS} layers",
+                               "quantized_layers": wl.n_linear, "audio_seconds_per_step_per_gpu": wl.units_per_step(),
+                               "encoder": "stand-in of FastConformer's shape (asrq_b200/conformer.py): NeMo's encoder body is not available"})
+        line["phases"] = wl.phases()
     if name == "c4":
         line["config"].update({"batch_per_gpu": wl.batch, "tokens": wl.STEPS, "layers": f"{wl.LAYERS}+{wl.LAYERS}",
                                "linearq_layers": wl.n_linear, "audio_seconds_per_step_per_gpu": wl.units_per_step()})
         line["phases"] = wl.phases()
     if rank == 0:
-        int8_tops = time_int8_peak(device) if name == "c2" else None
+        int8_tops = time_int8_peak(device) if name in ("c2", "c5") else None
         line["roofline"] = wl.roofline(kernel_ms, peaks, int8_tops)
         if e2e is not None:
             line["e2e"] = e2e
@@ -1089,7 +1310,7 @@ def main():
     ap.add_argument("--c4-tokens", type=int, default=None)
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 5 if args.workload == "c4" else 200
+        args.steps = 5 if args.workload in ("c4", "c5") else 200
     if args.warmup is None:
         args.warmup = 3
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -1118,11 +1339,11 @@ def main():
         torch.cuda.empty_cache()
     if world == 1 and not args.no_extra:
         also = []
-        for other in ("c1", "c2", "c3", "large", "c4"):
+        for other in ("c1", "c2", "c3", "large", "c5", "c4"):
             if other == args.workload:
                 continue
             try:
-                k = 3 if other == "c4" else 200
+                k = 3 if other in ("c4", "c5") else 200
                 w2, l2 = measure(other, args, rank, local_rank, world, device, peaks, k, 3, other != "large")
                 also.append(l2)
                 del w2

@@ -185,6 +185,23 @@ int asrq_add_rmsnorm(const void* x, const void* delta, const void* gamma, float 
 int asrq_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t inter, int dtype, void* stream);
 
 /*
+ * Between a fused q/k/v projection and the attention of a Qwen3 decoder block, in one launch: per-head RMS norm of queries
+ * and keys (weights q_weight, k_weight of head_dim values), rotary embedding from cos_table / sin_table (max_len x
+ * head_dim), and the write of the new keys and values into the caches.  Every step is rounded to `dtype` where the
+ * module sequence rounds it (Qwen3AttentionQ.forward of asrq/models/nemo/canary_qwen.py:89-120 runs the stock modules:
+ * norm in fp32 then cast, times weight, q * cos + rotate_half(q) * sin).
+ *   qkv      B*T rows of (n_q_heads + 2 n_kv_heads) * head_dim: queries, keys, values of one sequence position each;
+ *   q_out    B x n_q_heads x T x head_dim;
+ *   k_cache, v_cache   B x n_kv_heads x max_len x head_dim; row t of sequence b goes to position pos + t, where pos is
+ *            read from pos_device when that is not NULL (a decoding step replayed as a CUDA graph) and is the argument
+ *            otherwise.
+ * head_dim 64 or 128; qkv, q_out and the caches 8-byte aligned.
+ */
+int asrq_qk_norm_rope(const void* qkv, const void* q_weight, const void* k_weight, const void* cos_table, const void* sin_table,
+                      const int64_t* pos_device, int64_t pos, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T,
+                      int n_q_heads, int n_kv_heads, int head_dim, int64_t max_len, float eps, int dtype, void* stream);
+
+/*
  * The floating-point output head of a decoding step: y[M, N] = x[M, K] . w[N, K]^T, all of the 16-bit type `dtype`,
  * fp32 accumulation, for M <= 32 tokens and a vocabulary-sized N (any N >= 1).  The reference keeps these layers as
  * nn.Linear (proj_out, asrq/models/transformers/whisper.py:268; lm_head, asrq/models/nemo/canary_qwen.py:179); after

@@ -124,3 +124,48 @@ def test_dense_head(m, k, n, dtype):
     x2 = torch.randn(40, k, generator=gen).to(dtype).to(DEV)
     assert asrq_b200.dense_head(x2, w).shape == (40, n)
     asrq_b200.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,T,nq,nkv,hd,pos0,on_device", [(64, 1, 16, 8, 128, 37, True), (3, 9, 4, 2, 64, 0, False), (2, 5, 16, 8, 128, 11, False)])
+def test_qk_norm_rope(B, T, nq, nkv, hd, pos0, on_device, dtype):
+    """Against the module sequence (norm in fp32 then cast, times weight, q * cos + rotate_half(q) * sin, cache update) in
+    torch on the same device: values pass untouched, queries and keys agree to two units in the last place (the norm's
+    fp32 reduction order), nothing else in the caches is written."""
+    gen = torch.Generator().manual_seed(B + T + hd)
+    max_len, eps = 64, 1e-6
+    heads = nq + 2 * nkv
+    qkv = torch.randn(B * T, heads * hd, generator=gen).to(dtype).to(DEV)
+    qw = (1 + 0.1 * torch.randn(hd, generator=gen)).to(dtype).to(DEV)
+    kw = (1 + 0.1 * torch.randn(hd, generator=gen)).to(dtype).to(DEV)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    fr = torch.outer(torch.arange(max_len).float(), inv)
+    emb = torch.cat((fr, fr), -1)
+    cos, sin = emb.cos().to(dtype).to(DEV), emb.sin().to(dtype).to(DEV)
+    kc = torch.full((B, nkv, max_len, hd), 3.0, dtype=dtype, device=DEV)
+    vc = torch.full((B, nkv, max_len, hd), 3.0, dtype=dtype, device=DEV)
+    pos = torch.tensor([pos0], dtype=torch.long, device=DEV) if on_device else pos0
+    q = asrq_b200.qk_norm_rope(qkv, qw, kw, cos, sin, kc, vc, pos, B, T, nq, nkv, eps)
+
+    def rms(x, w):
+        f = x.float()
+        return w * (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).to(dtype)
+
+    def rope(x, c, s):
+        h = hd // 2
+        return x * c + torch.cat((-x[..., h:], x[..., :h]), -1) * s
+    v4 = qkv.view(B, T, heads, hd)
+    c, s = cos[pos0:pos0 + T], sin[pos0:pos0 + T]
+    q_ref = rope(rms(v4[:, :, :nq], qw).transpose(1, 2), c, s)
+    k_ref = rope(rms(v4[:, :, nq:nq + nkv], kw).transpose(1, 2), c, s)
+    v_ref = v4[:, :, nq + nkv:].transpose(1, 2)
+    ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+
+    def close(a, r):
+        return bool(((a.float() - r.float()).abs() <= 2 * ulp * r.float().abs().clamp_min(0.25)).all())
+    assert q.shape == (B, nq, T, hd) and close(q, q_ref)
+    assert close(kc[:, :, pos0:pos0 + T], k_ref)
+    assert torch.equal(vc[:, :, pos0:pos0 + T], v_ref)
+    untouched = torch.ones(max_len, dtype=torch.bool)
+    untouched[pos0:pos0 + T] = False
+    assert bool((kc[:, :, untouched.to(DEV)] == 3.0).all()) and bool((vc[:, :, untouched.to(DEV)] == 3.0).all())
