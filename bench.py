@@ -1155,6 +1155,10 @@ def measure(name, args, rank, local_rank, world, device, peaks, steps, warmup, f
     if name == "c4" and (args.c4_layers or args.c4_tokens):
         WhisperLargeV3.LAYERS = args.c4_layers or WhisperLargeV3.LAYERS
         WhisperLargeV3.STEPS = args.c4_tokens or WhisperLargeV3.STEPS
+    if name == "c5" and (args.c4_layers or args.c4_tokens):
+        CanaryQwenShape.ENC_LAYERS = args.c4_layers or CanaryQwenShape.ENC_LAYERS
+        CanaryQwenShape.DEC_LAYERS = args.c4_layers or CanaryQwenShape.DEC_LAYERS
+        CanaryQwenShape.STEPS = args.c4_tokens or CanaryQwenShape.STEPS
     wl = WORKLOADS[name](device, args.seed + 1000 * rank)
     parity = bool(wl.check_parity())
     if not parity:
@@ -1243,8 +1247,8 @@ def measure(name, args, rank, local_rank, world, device, peaks, steps, warmup, f
                    "M": getattr(wl, "M", None), "K": getattr(wl, "K", None), "N": getattr(wl, "N", None)},
         "parity_checked": parity, "kernel_ms": kernel_ms, "gpu_launches": launches * steps * reps, "clocks": clocks,
     }
-    if name == "c4" and (args.c4_layers or args.c4_tokens):
-        line["config"]["reduced"] = (f"NOT the benchmark configuration: {wl.LAYERS}+{wl.LAYERS} layers, {wl.STEPS} tokens "
+    if name in ("c4", "c5") and (args.c4_layers or args.c4_tokens):
+        line["config"]["reduced"] = (f"NOT the benchmark configuration: {args.c4_layers or 'all'} layers each, {wl.STEPS} tokens "
                                      "(a bounded run for profiler captures)")
     if name == "c5":
         line["config"].update({"batch_per_gpu": wl.batch, "tokens": wl.STEPS, "layers": f"{wl.ENC_LAYERS} blocks + {wl.DEC_LAYERS} layers",
@@ -1304,10 +1308,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the other workloads (the `also` rows)")
     ap.add_argument("--no-group", action="store_true", help="one step per CUDA graph instead of a graph of consecutive steps")
-    ap.add_argument("--c4-layers", type=int, default=None,
-                    help="workload c4 at reduced depth (encoder and decoder layers each) and, with --c4-tokens, fewer tokens: "
-                         "for bounded profiler captures; the line's config says so and it is not the benchmark")
-    ap.add_argument("--c4-tokens", type=int, default=None)
+    ap.add_argument("--c4-layers", "--layers", dest="c4_layers", type=int, default=None,
+                    help="whole-model workloads (c4, c5) at reduced depth (encoder and decoder layers each) and, with --tokens, "
+                         "fewer tokens: for bounded profiler captures; the line's config says so and it is not the benchmark")
+    ap.add_argument("--c4-tokens", "--tokens", dest="c4_tokens", type=int, default=None)
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 5 if args.workload in ("c4", "c5") else 200
