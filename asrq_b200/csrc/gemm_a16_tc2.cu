@@ -199,6 +199,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   const int helper = dpos >= 0 ? 1 + (dpos >> 2) : (warp >= kT2FirstEpilogueWarp ? 0 : -1);  // position among the drainers
   // y = accumulator + bias for chunks ch0, ch0 + step, ... (32 tokens each) of `unit`'s tile, this warp's 32 features
   auto drain = [&](int unit, uint32_t buf, int ch0, int step) {
+    __syncwarp();  // the tensor-memory loads are warp-wide instructions: the lanes come out of a polling loop
     const int fp = unit % p.n_fpairs, tt = unit / p.n_fpairs;
     const int f = (2 * fp + int(rank)) * 128 + (warp & 3) * 32 + lane;
     t2_drain<BF16>(p.y + size_t(tt) * p.bt * p.N + f, p.N, p.M - tt * p.bt, p.bt / 32,
@@ -207,7 +208,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
   };
   // a helper that is not an epilogue warp: wait for the last unit's accumulator, drain its share
   auto help_drain = [&]() {
-    if (helper > 0 && tc::mbar_wait(fin_bar, 0u, p.status, 8)) {
+    if (helper > 0 && __all_sync(0xffffffffu, tc::mbar_wait(fin_bar, 0u, p.status, 8))) {
       tc::fence_after_sync();
       drain(last_unit, uint32_t(my_units - 1) & 1u, helper, kT2Drainers);
     }
@@ -357,17 +358,26 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
       if (dpos == 0) T2_MARK(1, titer, 0);
       {
         const uint32_t got = tc::mbar_try_wait2(afree_bar(a), aph ^ 1u, wfull_bar(s), ph);
-        if (!(got & 1u) && !tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7)) break;
-        if (!(got & 2u) && !tc::mbar_wait(wfull_bar(s), ph, p.status, 5)) break;
+        bool okw = true;
+        if (!(got & 1u)) okw = tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7);
+        if (okw && !(got & 2u)) okw = tc::mbar_wait(wfull_bar(s), ph, p.status, 5);
+        // one decision for the warp (a wait that gave up ends the loop for all its lanes: the warp-wide operations
+        // below need every lane), and the lanes are together again from here on
+        if (!__all_sync(0xffffffffu, okw)) break;
       }
       if (dpos == 0) T2_MARK(1, titer, 2);
       constexpr int NV = BITS / 2;  // 16-byte vectors of packed weights per row per K block
       uint4 qv[NV];
 #pragma unroll
       for (int v = 0; v < NV; ++v) qv[v] = tc::ld_shared_v4(base + w_ring + s * kT2WSlotBytes + t * (8 * BITS) + v * 16);
-      // The packed-weight slot is free once every lane holds its words.  A shared-memory load instruction returns all
-      // lanes' data together, so lane 0's arrival, made to depend on its own last word, comes after all of them.
-      if (lane == 0) tc::mbar_arrive_after(wfree_bar(s), qv[NV - 1].w);
+      // The packed-weight slot is free once EVERY lane holds its words.  The lanes may have come out of the barrier
+      // waits above at different times (a lane that saw the phase complete in the combined test skips the waiting
+      // loop), so they are brought together and the arrival is made to depend on a warp-wide reduction over the words
+      // every lane loaded: it cannot be issued before all of those loads have returned.
+      {
+        const uint32_t dep = __reduce_or_sync(0xffffffffu, qv[0].x | qv[NV - 1].w);
+        if (lane == 0) tc::mbar_arrive_after(wfree_bar(s), dep);
+      }
       // 128-byte swizzle: 16-byte chunk c of row t lives at chunk position c ^ (t % 8); the row start is 128-byte
       // aligned, so the position is an XOR on the address
       const uint32_t arow = (base + a * kT2ATileBytes + t * 128) | uint32_t((t & 7) << 4);
@@ -405,7 +415,7 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
     for (int unit = cluster; unit < nunits && ok; unit += nclusters, ++ucount) {
       const uint32_t buf = ucount & 1u, aph = (ucount >> 1) & 1u;
       if (warp == kT2FirstEpilogueWarp) T2_MARK(2, ucount, 0);
-      if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, tc::mbar_wait(accf_bar(buf), aph, p.status, 6))) { ok = false; break; }
       if (warp == kT2FirstEpilogueWarp) T2_MARK(2, ucount, 1);
       tc::fence_after_sync();
       if (unit == last_unit) {

@@ -742,13 +742,17 @@ class WhisperLargeV3(Workload):
         y = L(h)
         rows = torch.arange(0, h.shape[0], max(1, h.shape[0] // 256))
         w, s, z, b = L.weight.cpu(), L.scales.cpu(), L.zeros.cpu(), L.bias.cpu()
-        ok = _rows_ok(y[rows.to(self.dev)], O.linearq_forward_fp32(h[rows.to(self.dev)].cpu(), w, s, z, b, 4, 128))
+        ok1 = _rows_ok(y[rows.to(self.dev)], O.linearq_forward_fp32(h[rows.to(self.dev)].cpu(), w, s, z, b, 4, 128))
         hb = h[:self.batch].contiguous()
-        ok = ok and _rows_ok(L(hb), O.linearq_forward_fp32(hb.cpu(), w, s, z, b, 4, 128))
+        ok2 = _rows_ok(L(hb), O.linearq_forward_fp32(hb.cpu(), w, s, z, b, 4, 128))
         nb = min(self.batch, 4)
         a_ = eng.generate(x[:nb], steps=6, use_graph=False).clone()
         b_ = eng.generate(x[:nb], steps=6, use_graph=True).clone()
-        return ok and torch.equal(a_, b_)
+        ok3 = torch.equal(a_, b_)
+        if not (ok1 and ok2 and ok3):
+            print(f"bench.py c4 parity on {self.dev}: encoder-sized call {ok1}, decode-sized call {ok2}, graph == eager {ok3}",
+                  file=sys.stderr, flush=True)
+        return ok1 and ok2 and ok3
 
     def e2e_step(self, i):
         xh = self.x_host[i % self.nsets]
