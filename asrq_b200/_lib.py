@@ -61,6 +61,8 @@ SIGNATURES = {
     "asrq_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "asrq_qk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                   c_int64, c_int64, c_int, c_int, c_int, c_int64, ctypes.c_float, c_int, c_void_p]),
+    "asrq_decode_self_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, ctypes.c_float,
+                                           c_int, c_void_p]),
     "asrq_dense_head": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "asrq_rtn_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                               c_void_p]),

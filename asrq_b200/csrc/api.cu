@@ -34,6 +34,8 @@ int hadamard_fold(const void* w, int w_dtype, float* out, int64_t N, int64_t K, 
 int qk_norm_rope(const void* qkv, const void* qw, const void* kw, const void* cos_t, const void* sin_t, const long long* pos_dev,
                  long long pos_host, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int nq, int nkv, int hd,
                  int64_t max_len, float eps, int dtype, cudaStream_t stream);
+int decode_self_attention(const void* qkv, void* kv, const long long* pos_dev, void* out, int64_t B, int H, int hd, int64_t max_len,
+                          float scale, int dtype, cudaStream_t stream);
 int dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, int sm_count, cudaStream_t stream);
 int hadamard_quant_int4(const void* x, uint8_t* qa, float* sa, int64_t M, int64_t K, int hadamard, int dtype,
                         int out_int8, cudaStream_t stream);
@@ -461,6 +463,23 @@ int asrq_qk_norm_rope(const void* qkv, const void* q_weight, const void* k_weigh
   if (B == 0) return ASRQ_OK;
   return qk_norm_rope(qkv, q_weight, k_weight, cos_table, sin_table, reinterpret_cast<const long long*>(pos_device), (long long)pos, q_out,
                       k_cache, v_cache, B, T, n_q_heads, n_kv_heads, head_dim, max_len, eps, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int asrq_decode_self_attention(const void* qkv, void* kv_cache, const int64_t* pos_device, void* out, int64_t B, int n_heads,
+                               int head_dim, int64_t max_len, float scale, int dtype, void* stream) {
+  last_error().clear();
+  if (!qkv || !kv_cache || !pos_device || !out) return fail(ASRQ_ERR_NULL, "asrq_decode_self_attention: no argument may be NULL");
+  if (dtype != ASRQ_F16 && dtype != ASRQ_BF16) return fail(ASRQ_ERR_DTYPE, "asrq_decode_self_attention: dtype %d", dtype);
+  if (B < 0 || n_heads <= 0 || (head_dim != 64 && head_dim != 128) || max_len <= 0 || max_len > 512 || B * n_heads > (int64_t(1) << 28))
+    return fail(ASRQ_ERR_SHAPE, "asrq_decode_self_attention: B=%lld heads=%d head_dim=%d (64 or 128) max_len=%lld (at most 512)",
+                (long long)B, n_heads, head_dim, (long long)max_len);
+  if (!aligned16(kv_cache)) return fail(ASRQ_ERR_ALIGN, "asrq_decode_self_attention: kv_cache must be 16-byte aligned");
+  const DeviceFacts* f;
+  int rc;
+  if ((rc = device_facts(&f))) return rc;
+  if (B == 0) return ASRQ_OK;
+  return decode_self_attention(qkv, kv_cache, reinterpret_cast<const long long*>(pos_device), out, B, n_heads, head_dim, max_len, scale,
+                               dtype, static_cast<cudaStream_t>(stream));
 }
 
 int asrq_dense_head(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int dtype, void* stream) {

@@ -12,6 +12,10 @@
 //                   per-head RMS norm of queries and keys, the rotary embedding, and the write of the new keys and
 //                   values into the caches at the sequence position (read from device memory when decoding under a
 //                   graph), every step rounded to 16 bits where the module sequence rounds it;
+//   decode_self_attention   one new token per sequence against its own cache (multi-head, one warp per sequence and
+//                   head): the new key and value are written at the position read from device memory, then
+//                   softmax(q . K^T) . V over positions 0..pos in fp32 -- the cache write and the attention of a
+//                   decoder step's self-attention in one launch of this library's chain;
 //   epilogue16      y = act(y) or y = residual + y on an already written output: the fall-back for
 //                   layers whose kernel does not fuse the epilogue.
 //
@@ -308,6 +312,106 @@ qk_norm_rope_kernel(const uint16_t* __restrict__ qkv, const uint16_t* __restrict
   }
 }
 
+// qkv: B rows of [q | k | v], each H * hd wide.  kv: (2, B, H, max_len, hd) keys then values.  out: B x (H * hd).
+// E = hd / 32 elements per lane.  Scores: lane j takes keys j, j + 32, ... (q from shared memory); output: lane owns E
+// consecutive elements of the head, probabilities broadcast by shuffle.
+template <int E>
+__global__ void __launch_bounds__(128)
+decode_self_attention_kernel(const uint16_t* __restrict__ qkv, uint16_t* __restrict__ kv, const long long* __restrict__ pos_dev,
+                             uint16_t* __restrict__ out, int B, int H, int max_len, float scale, int bf16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr int hd = 32 * E;
+  constexpr int kWarps = 4;
+  constexpr int kMaxKeysPerLane = 16;  // max_len <= 512
+  __shared__ float qs[kWarps][hd];
+  __shared__ float ps[kWarps][32 * kMaxKeysPerLane + 16];  // probabilities by key; the tail stays zero
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int item = blockIdx.x * kWarps + wib;
+  if (item >= B * H) return;
+  const int b = item / H, h = item - b * H;
+  const int pos = int(*pos_dev);
+  const size_t d = size_t(H) * hd;
+  const uint16_t* row = qkv + size_t(b) * 3 * d + size_t(h) * hd;
+  uint16_t* kc = kv + ((size_t(b) * H + h) * max_len) * hd;
+  uint16_t* vc = kc + size_t(B) * H * max_len * hd;
+  // the new key and value into the cache, the query (scaled) into shared memory
+#pragma unroll
+  for (int i = 0; i < E; ++i) {
+    const int e = lane * E + i;
+    qs[wib][e] = in16(row[e], bf16) * scale;
+    kc[size_t(pos) * hd + e] = row[d + e];
+    vc[size_t(pos) * hd + e] = row[2 * d + e];
+  }
+  __syncwarp();
+  // scores of this lane's keys
+  float sc[kMaxKeysPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kMaxKeysPerLane; ++j) {
+    const int t = lane + 32 * j;
+    sc[j] = -INFINITY;
+    if (t <= pos) {
+      const uint4* kr = reinterpret_cast<const uint4*>(kc + size_t(t) * hd);
+      float acc = 0.f;
+#pragma unroll
+      for (int c = 0; c < hd / 8; ++c) {
+        const uint4 u = kr[c];
+        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          acc = fmaf(qs[wib][c * 8 + 2 * m], in16(uint16_t(w4[m] & 0xffffu), bf16), acc);
+          acc = fmaf(qs[wib][c * 8 + 2 * m + 1], in16(uint16_t(w4[m] >> 16), bf16), acc);
+        }
+      }
+      sc[j] = acc;
+      mx = fmaxf(mx, acc);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMaxKeysPerLane; ++j) {
+    sc[j] = (lane + 32 * j <= pos) ? __expf(sc[j] - mx) : 0.f;
+    sum += sc[j];
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+  // output: probabilities through shared memory (read as broadcasts), every lane accumulates its E elements of the head;
+  // sixteen value rows are requested before the first is used, so their latencies overlap
+#pragma unroll
+  for (int j = 0; j < kMaxKeysPerLane; ++j) ps[wib][lane + 32 * j] = sc[j];
+  __syncwarp();
+  if (lane < 16) ps[wib][32 * kMaxKeysPerLane + lane] = 0.f;
+  __syncwarp();
+  float o_acc[E];
+#pragma unroll
+  for (int i = 0; i < E; ++i) o_acc[i] = 0.f;
+  for (int t0 = 0; t0 <= pos; t0 += 16) {  // warp-uniform
+    uint32_t vv[16][E / 2];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int t = min(t0 + u, pos);  // rows past the position repeat the last one; their probability is zero
+      const uint32_t* vr = reinterpret_cast<const uint32_t*>(vc + size_t(t) * hd + lane * E);
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) vv[u][i] = vr[i];
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const float pr = ps[wib][t0 + u];
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) {
+        o_acc[2 * i] = fmaf(pr, in16(uint16_t(vv[u][i] & 0xffffu), bf16), o_acc[2 * i]);
+        o_acc[2 * i + 1] = fmaf(pr, in16(uint16_t(vv[u][i] >> 16), bf16), o_acc[2 * i + 1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < E; ++i) out[size_t(b) * d + size_t(h) * hd + lane * E + i] = float_to_out16(o_acc[i] * inv, bf16);
+}
+
 __global__ void __launch_bounds__(256)
 epilogue16_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ residual, size_t n_vec, int act, int bf16) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -397,6 +501,17 @@ int qk_norm_rope(const void* qkv, const void* qw, const void* kw, const void* co
                       o(k_cache), o(v_cache), int(B * T), int(T), nq, nkv, int(max_len), eps, bf16);
   return launch_pdl(qk_norm_rope_kernel<2>, grid, block, stream, p(qkv), p(qw), p(kw), p(cos_t), p(sin_t), pos_dev, pos_host, o(q_out),
                     o(k_cache), o(v_cache), int(B * T), int(T), nq, nkv, int(max_len), eps, bf16);
+}
+
+int decode_self_attention(const void* qkv, void* kv, const long long* pos_dev, void* out, int64_t B, int H, int hd, int64_t max_len,
+                          float scale, int dtype, cudaStream_t stream) {
+  const dim3 grid(unsigned((B * H + 3) / 4)), block(128);
+  const int bf16 = dtype == ASRQ_BF16;
+  if (hd == 64)
+    return launch_pdl(decode_self_attention_kernel<2>, grid, block, stream, static_cast<const uint16_t*>(qkv), static_cast<uint16_t*>(kv),
+                      pos_dev, static_cast<uint16_t*>(out), int(B), H, int(max_len), scale, bf16);
+  return launch_pdl(decode_self_attention_kernel<4>, grid, block, stream, static_cast<const uint16_t*>(qkv), static_cast<uint16_t*>(kv),
+                    pos_dev, static_cast<uint16_t*>(out), int(B), H, int(max_len), scale, bf16);
 }
 
 // y = act(y) / y = residual + y over M x N 16-bit elements (M*N a multiple of 8, pointers 16-byte aligned)

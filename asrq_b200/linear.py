@@ -134,6 +134,20 @@ def qk_norm_rope(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tens
     return q
 
 
+def decode_self_attention(qkv: torch.Tensor, kv_cache: torch.Tensor, pos: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Self-attention of one decoding step with the cache write: ``qkv`` (B, 3 * d) from a fused projection, ``kv_cache``
+    (2, B, heads, max_len, head_dim), ``pos`` a one-element int64 CUDA tensor (the new token's position).  Returns (B, d)."""
+    dt = _require_cuda_16bit(qkv, "decode_self_attention")
+    _, B, H, max_len, hd = kv_cache.shape
+    q2 = qkv.reshape(B, 3 * H * hd)
+    q2 = q2 if q2.is_contiguous() else q2.contiguous()
+    out = torch.empty((B, H * hd), dtype=qkv.dtype, device=qkv.device)
+    with _on_device(qkv.device):
+        _lib.call("asrq_decode_self_attention", q2.data_ptr(), kv_cache.data_ptr(), pos.data_ptr(), out.data_ptr(), B, H, hd, max_len,
+                  float(scale), dt, torch.cuda.current_stream(qkv.device).cuda_stream)
+    return out
+
+
 def dense_head(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """``x @ weight.T`` for the floating-point output head of a decoding step (``weight`` is (vocabulary, K) in the
     activations' 16-bit type): this library's kernel for up to 32 rows of ``x`` and K a multiple of 32 up to 3200,

@@ -21,6 +21,7 @@ Two things live here.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -29,7 +30,7 @@ import torch.nn.functional as F
 
 from . import packing
 from .convert import linearq_from_linear
-from .linear import LinearQ, add_layernorm, dense_head
+from .linear import LinearQ, add_layernorm, decode_self_attention, dense_head
 
 try:  # the model classes need transformers; the engine does not
     from transformers.models.whisper.modeling_whisper import (WhisperAttention, WhisperConfig, WhisperDecoder,
@@ -211,6 +212,8 @@ class WhisperEngine:
     End-of-sequence is not interpreted: every utterance runs ``steps`` tokens (callers cut at the first
     end-of-sequence id), which is also how the throughput benchmark wants it.
     """
+
+    fused_self_attention = os.environ.get("ASRQ_B200_WHISPER_FUSED_SELF_ATTENTION", "1") == "1"
 
     def __init__(self, config, device, dtype=torch.float16):
         self.cfg = config
@@ -402,17 +405,21 @@ class WhisperEngine:
         b = self.tok.shape[0]
         hd = self.d // self.heads_d
         scaling = hd ** -0.5
-        self.mask.index_fill_(3, self.pos, 0.0)
+        if not self.fused_self_attention:
+            self.mask.index_fill_(3, self.pos, 0.0)
         x = (self.embed[self.tok] + self.dec_pos[self.pos]).unsqueeze(1)  # (B, 1, d)
         for i, L in enumerate(self.dec_layers):
             h = L["ln1"](x)
             qkv = L["qkv"](h)
-            q = qkv[..., :self.d]
-            if not L["q_folded"]:
-                q = q * scaling
-            # this position's key and value into the cache: one copy for both
-            self.kv_self[i].index_copy_(3, self.pos, qkv[..., self.d:].view(b, 1, 2, self.heads_d, hd).permute(2, 0, 3, 1, 4))
-            a = self._attend(q, self.kv_self[i, 0], self.kv_self[i, 1], self.heads_d, self.mask)
+            if self.fused_self_attention:
+                # this position's key and value into the cache and the attention over the cache: one kernel
+                a = decode_self_attention(qkv, self.kv_self[i], self.pos, 1.0 if L["q_folded"] else scaling).unsqueeze(1)
+            else:
+                q = qkv[..., :self.d]
+                if not L["q_folded"]:
+                    q = q * scaling
+                self.kv_self[i].index_copy_(3, self.pos, qkv[..., self.d:].view(b, 1, 2, self.heads_d, hd).permute(2, 0, 3, 1, 4))
+                a = self._attend(q, self.kv_self[i, 0], self.kv_self[i, 1], self.heads_d, self.mask)
             x = L["out"].forward_fused(a, residual=x)
             h = L["lnx"](x)
             q = L["xq"](h)

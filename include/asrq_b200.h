@@ -202,6 +202,19 @@ int asrq_qk_norm_rope(const void* qkv, const void* q_weight, const void* k_weigh
                       int n_q_heads, int n_kv_heads, int head_dim, int64_t max_len, float eps, int dtype, void* stream);
 
 /*
+ * The self-attention of one decoding step (multi-head, one new token per sequence), cache write included: for every
+ * sequence b and head h the new key and value (from the fused projection's output row) are stored at position *pos_device
+ * of the cache, then out = softmax(scale * q . K[0..pos]^T) . V[0..pos] with fp32 scores, softmax and accumulation.
+ * In the reference this is the stock attention module behind WhisperAttentionQ's projections plus its cache update
+ * (asrq/models/transformers/whisper.py:38-97 runs the parent class's forward).
+ *   qkv       B rows of [q | k | v], each n_heads * head_dim wide, type `dtype`;
+ *   kv_cache  (2, B, n_heads, max_len, head_dim): keys, then values; 16-byte aligned; max_len <= 512;
+ *   out       B x (n_heads * head_dim);  head_dim 64 or 128;  pos_device: one int64 in device memory, < max_len.
+ */
+int asrq_decode_self_attention(const void* qkv, void* kv_cache, const int64_t* pos_device, void* out, int64_t B, int n_heads,
+                               int head_dim, int64_t max_len, float scale, int dtype, void* stream);
+
+/*
  * The floating-point output head of a decoding step: y[M, N] = x[M, K] . w[N, K]^T, all of the 16-bit type `dtype`,
  * fp32 accumulation, for M <= 32 tokens and a vocabulary-sized N (any N >= 1).  The reference keeps these layers as
  * nn.Linear (proj_out, asrq/models/transformers/whisper.py:268; lm_head, asrq/models/nemo/canary_qwen.py:179); after

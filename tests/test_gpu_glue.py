@@ -169,3 +169,30 @@ def test_qk_norm_rope(B, T, nq, nkv, hd, pos0, on_device, dtype):
     untouched = torch.ones(max_len, dtype=torch.bool)
     untouched[pos0:pos0 + T] = False
     assert bool((kc[:, :, untouched.to(DEV)] == 3.0).all()) and bool((vc[:, :, untouched.to(DEV)] == 3.0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,hd,max_len,pos0,scale", [(32, 20, 64, 129, 0, 1.0), (32, 20, 64, 129, 77, 1.0), (3, 4, 128, 40, 39, 0.5),
+                                                       (5, 6, 64, 448, 300, 0.125)])
+def test_decode_self_attention(B, H, hd, max_len, pos0, scale, dtype):
+    """Against the cache update plus scaled_dot_product_attention in fp32 on the same values: the new key and value land at
+    the position (nothing else in the cache moves), the output is one rounding of the fp32 result."""
+    gen = torch.Generator().manual_seed(B * H + pos0)
+    d = H * hd
+    qkv = torch.randn(B, 3 * d, generator=gen).to(dtype).to(DEV)
+    kv = torch.randn(2, B, H, max_len, hd, generator=gen).to(dtype).to(DEV)
+    before = kv.clone()
+    pos = torch.tensor([pos0], dtype=torch.long, device=DEV)
+    out = asrq_b200.decode_self_attention(qkv, kv, pos, scale)
+    k_new = qkv[:, d:2 * d].view(B, H, hd)
+    v_new = qkv[:, 2 * d:].view(B, H, hd)
+    assert torch.equal(kv[0, :, :, pos0], k_new) and torch.equal(kv[1, :, :, pos0], v_new)
+    keep = torch.ones(max_len, dtype=torch.bool, device=DEV)
+    keep[pos0] = False
+    assert torch.equal(kv[:, :, :, keep], before[:, :, :, keep])
+    q = qkv[:, :d].view(B, H, 1, hd).float()
+    ref = F.scaled_dot_product_attention(q, kv[0, :, :, :pos0 + 1].float(), kv[1, :, :, :pos0 + 1].float(), scale=scale)
+    ref = ref.reshape(B, d)
+    ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+    err = (out.float() - ref).abs()
+    assert bool((err <= 0.6 * ulp * ref.abs().clamp_min(1.0) + 1e-6).all()), float(err.max())
