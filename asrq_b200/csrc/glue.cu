@@ -43,9 +43,19 @@ add_layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
                      const uint16_t* __restrict__ beta, float eps, uint16_t* __restrict__ x_out, uint16_t* __restrict__ h_out,
                      int rows, int dim, int bf16) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * kLnWarps + (threadIdx.x >> 5);
+  // the norm's weight and bias are constants: fetched ahead of the stream dependency (vector path)
+  uint4 gpre[VEC > 0 ? VEC : 1], bpre[VEC > 0 ? VEC : 1];
+  if constexpr (VEC > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int e = (i * 32 + lane) * 8;
+      gpre[i] = __ldg(reinterpret_cast<const uint4*>(gamma + e));
+      bpre[i] = __ldg(reinterpret_cast<const uint4*>(beta + e));
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (row >= rows) return;
   const size_t off = size_t(row) * dim;
   if constexpr (VEC > 0) {
@@ -93,8 +103,7 @@ add_layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int e = (i * 32 + lane) * 8;
-      const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma + e));
-      const uint4 b = __ldg(reinterpret_cast<const uint4*>(beta + e));
+      const uint4 g = gpre[i], b = bpre[i];
       const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, bw[4] = {b.x, b.y, b.z, b.w};
       uint32_t ow[4];
 #pragma unroll
