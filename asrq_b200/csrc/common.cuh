@@ -154,6 +154,39 @@ __device__ __forceinline__ uint16_t epilogue16(uint16_t y16, int act, bool has_r
   if (has_res) y16 = float_to_out16(out16_to_float(res16, bf16) + out16_to_float(y16, bf16), bf16);
   return y16;
 }
+// ---- layer norm of a row held by one warp as VEC 16-byte vectors per lane (dim = 256 * VEC) --------------------
+// raw[i] holds elements (i * 32 + lane) * 8 .. + 7 of the row; statistics in fp32, two passes.
+template <int VEC>
+__device__ __forceinline__ void ln_row_stats(const uint4 (&raw)[VEC], int dim, float eps, bool bf16, float& mean, float& rstd) {
+  auto val = [&](int i, int e) {
+    const uint32_t w = e < 2 ? raw[i].x : (e < 4 ? raw[i].y : (e < 6 ? raw[i].z : raw[i].w));
+    const uint16_t h = uint16_t((e & 1) ? (w >> 16) : (w & 0xffffu));
+    return out16_to_float(h, bf16);
+  };
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum += val(i, e);
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  mean = sum / float(dim);
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float d = val(i, e) - mean;
+      sq = fmaf(d, d, sq);
+    }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  rstd = rsqrtf(sq / float(dim) + eps);
+}
+__device__ __forceinline__ float ln_apply(float v, float mean, float rstd, float g, float b) {
+  return fmaf((v - mean) * rstd, g, b);
+}
+
 // the fp32 result of a layer (bias already added) through rounding and the epilogue
 __device__ __forceinline__ uint16_t finish16(float v, int act, const uint16_t* residual, size_t idx, bool bf16) {
   const uint16_t y16 = float_to_out16(v, bf16);

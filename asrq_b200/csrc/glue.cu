@@ -59,57 +59,43 @@ add_layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
   if (row >= rows) return;
   const size_t off = size_t(row) * dim;
   if constexpr (VEC > 0) {
-    float v[VEC > 0 ? VEC * 8 : 1];
+    uint4 xr[VEC > 0 ? VEC : 1];  // the row (after the add, rounded to 16 bits), as the statistics see it
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int e = (i * 32 + lane) * 8;
       const uint4 a = *reinterpret_cast<const uint4*>(x + off + e);
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-      uint32_t dw[4] = {0, 0, 0, 0};
       if (delta) {
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
         const uint4 d = *reinterpret_cast<const uint4*>(delta + off + e);
-        dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w;
-      }
-      uint32_t ow[4];
+        const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+        uint32_t ow[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float lo = in16(uint16_t(aw[j] & 0xffffu), bf16), hi = in16(uint16_t(aw[j] >> 16), bf16);
-        if (delta) {
-          lo += in16(uint16_t(dw[j] & 0xffffu), bf16);
-          hi += in16(uint16_t(dw[j] >> 16), bf16);
+        for (int j = 0; j < 4; ++j) {
+          const float lo = in16(uint16_t(aw[j] & 0xffffu), bf16) + in16(uint16_t(dw[j] & 0xffffu), bf16);
+          const float hi = in16(uint16_t(aw[j] >> 16), bf16) + in16(uint16_t(dw[j] >> 16), bf16);
+          ow[j] = uint32_t(float_to_out16(lo, bf16)) | (uint32_t(float_to_out16(hi, bf16)) << 16);
         }
-        const uint16_t lo16 = float_to_out16(lo, bf16), hi16 = float_to_out16(hi, bf16);
-        ow[j] = uint32_t(lo16) | (uint32_t(hi16) << 16);
-        v[i * 8 + 2 * j] = in16(lo16, bf16);
-        v[i * 8 + 2 * j + 1] = in16(hi16, bf16);
+        xr[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      } else {
+        xr[i] = a;
       }
-      if (x_out) *reinterpret_cast<uint4*>(x_out + off + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      if (x_out) *reinterpret_cast<uint4*>(x_out + off + e) = xr[i];
     }
-    float sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < VEC * 8; ++i) sum += v[i];
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float mean = sum / float(dim);
-    float sq = 0.f;
-#pragma unroll
-    for (int i = 0; i < VEC * 8; ++i) {
-      const float d = v[i] - mean;
-      sq = fmaf(d, d, sq);
-    }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    const float rstd = rsqrtf(sq / float(dim) + eps);
+    float mean, rstd;
+    ln_row_stats<(VEC > 0 ? VEC : 1)>(xr, dim, eps, bf16 != 0, mean, rstd);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int e = (i * 32 + lane) * 8;
       const uint4 g = gpre[i], b = bpre[i];
+      const uint32_t xw[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
       const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, bw[4] = {b.x, b.y, b.z, b.w};
       uint32_t ow[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float lo = (v[i * 8 + 2 * j] - mean) * rstd * in16(uint16_t(gw[j] & 0xffffu), bf16) + in16(uint16_t(bw[j] & 0xffffu), bf16);
-        const float hi = (v[i * 8 + 2 * j + 1] - mean) * rstd * in16(uint16_t(gw[j] >> 16), bf16) + in16(uint16_t(bw[j] >> 16), bf16);
+        const float lo = ln_apply(in16(uint16_t(xw[j] & 0xffffu), bf16), mean, rstd, in16(uint16_t(gw[j] & 0xffffu), bf16),
+                                  in16(uint16_t(bw[j] & 0xffffu), bf16));
+        const float hi = ln_apply(in16(uint16_t(xw[j] >> 16), bf16), mean, rstd, in16(uint16_t(gw[j] >> 16), bf16),
+                                  in16(uint16_t(bw[j] >> 16), bf16));
         ow[j] = uint32_t(float_to_out16(lo, bf16)) | (uint32_t(float_to_out16(hi, bf16)) << 16);
       }
       *reinterpret_cast<uint4*>(h_out + off + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
