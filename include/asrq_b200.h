@@ -17,10 +17,10 @@
  *     synchronises, so all of them are safe on any stream;
  *   - the buffers' device must be the CURRENT device of the calling thread (the library reads
  *     cudaGetDevice for its per-device facts and launches there);
- *   - constant operands (packed weights, scales, zeros, bias) must be complete in memory before
- *     the call is ENQUEUED, not merely ordered before it on the stream: the decode kernels are
- *     launched with programmatic dependent launch and fetch these operands before they wait for
- *     the preceding kernel on the stream.  After writing or repacking weights on a stream,
+ *   - constant operands (packed weights, scales, zeros, bias; a layer norm's weight and bias; the
+ *     output head's matrix) must be complete in memory before the call is ENQUEUED, not merely
+ *     ordered before it on the stream: the kernels are launched with programmatic dependent launch
+ *     and fetch these operands before they wait for the preceding kernel on the stream.  After writing or repacking weights on a stream,
  *     synchronise that stream once (or set option "no_pdl") before the first call that uses them.
  *     Activations, outputs and the workspace carry ordinary stream ordering;
  *   - all matrices are row-major and contiguous.  `dtype` selects the 16-bit
