@@ -5,8 +5,8 @@
 // costs (set-up, first TMA and first dequantisation pass before the first MMA, an epilogue nothing
 // overlaps): 10-15 us for a 1-3 MB layer either way.  This kernel is built for a CHAIN of such layers:
 //
-//   * a block owns ONE work item -- a 128-feature tile and a part of K of at most 7 blocks of 64 -- so all
-//     of its packed weights (<= 28 KB) and all of its activation tiles fit shared memory at once;
+//   * a block owns ONE work item -- a 128-feature tile and a part of K of at most 12 blocks of 64 -- so all
+//     of its packed weights (<= 48 KB) and all of its activation tiles fit shared memory at once;
 //   * it triggers its dependents as its first instruction and is small enough (448 threads, <= 73
 //     registers, < 113 KB) for two launches to share an SM.  Packed weights are fetched by TMA and the
 //     first three K blocks are dequantised BEFORE griddepcontrol.wait: weights do not depend on the
@@ -36,7 +36,7 @@ namespace {
 
 constexpr int kSkWarps = 14;
 constexpr int kSkThreads = 32 * kSkWarps;
-constexpr int kSkMaxKb = 10;                    // K blocks of 64 per work item
+constexpr int kSkMaxKb = 12;                    // K blocks of 64 per work item
 constexpr int kSkMaxSplit = 8;
 constexpr uint32_t kSkATile = 128 * 128;        // one dequantised A slot: 128 rows x 64 16-bit elements
 constexpr uint32_t kSkWSlot = 4096;             // packed weights of one K block (<= 128 x 32 B)
