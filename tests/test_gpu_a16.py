@@ -495,12 +495,13 @@ def test_mid_m_tensor_core_kernel(bits, g, m, k, n, bias, dtype):
         assert float(((y.float().cpu() - y_old.float().cpu()).abs() / scale).max()) < 4e-3
 
 
-def test_mid_kernel_takes_the_qwen3_down_projection_at_64_tokens():
+@pytest.mark.parametrize("m", [20, 64])
+def test_mid_kernel_takes_the_qwen3_down_projection(m):
     """K = 6144 is 96 K blocks: eight parts of twelve.  Against the fp32 oracle and, bit for bit, two runs of itself."""
-    case = O.make_c3(seed=11, m=64, k=6144, n=2048, bits=4, group_size=128)
+    case = O.make_c3(seed=11, m=m, k=6144, n=2048, bits=4, group_size=128)
     y = run_a16_abi("asrq_w4a16_gemm", case)
-    assert_close_rows(y, _ref32(case), what="down projection m64")
+    assert_close_rows(y, _ref32(case), what=f"down projection m{m}")
     assert torch.equal(y, run_a16_abi("asrq_w4a16_gemm", case))
     with lib_option("mid_kernel", 1):
         y_old = run_a16_abi("asrq_w4a16_gemm", case)
-    assert_close_rows(y_old, _ref32(case), what="down projection m64, split-K kernel")
+    assert_close_rows(y_old, _ref32(case), what=f"down projection m{m}, other kernels")
