@@ -214,6 +214,7 @@ class WhisperEngine:
     """
 
     fused_self_attention = os.environ.get("ASRQ_B200_WHISPER_FUSED_SELF_ATTENTION", "1") == "1"
+    cross_kv_views = os.environ.get("ASRQ_B200_WHISPER_CROSS_KV_VIEWS", "1") == "1"
 
     def __init__(self, config, device, dtype=torch.float16):
         self.cfg = config
@@ -377,8 +378,16 @@ class WhisperEngine:
         dev, dt, nl = self.device, self.dtype, len(self.dec_layers)
         hd = self.d // self.heads_d
         self.kv_self = torch.zeros(nl, 2, batch, self.heads_d, max_len, hd, device=dev, dtype=dt)  # keys, values
-        self.k_cross = torch.empty(nl, batch, self.heads_d, src_len, hd, device=dev, dtype=dt)
-        self.v_cross = torch.empty_like(self.k_cross)
+        if self.cross_kv_views:
+            # the cross-attention keys and values stay where the fused projection wrote them, (B, T, [k | v]); the attention
+            # reads them through head-major views (128-byte runs per head and position)
+            self.xkv = torch.empty(nl, batch, src_len, 2 * self.d, device=dev, dtype=dt)
+            kv = self.xkv.view(nl, batch, src_len, 2, self.heads_d, hd)
+            self.k_cross = kv[:, :, :, 0].permute(0, 1, 3, 2, 4)   # (layer, B, H, T, hd) views
+            self.v_cross = kv[:, :, :, 1].permute(0, 1, 3, 2, 4)
+        else:
+            self.k_cross = torch.empty(nl, batch, self.heads_d, src_len, hd, device=dev, dtype=dt)
+            self.v_cross = torch.empty_like(self.k_cross)
         self.tok = torch.zeros(batch, dtype=torch.long, device=dev)      # token fed to the next step
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)          # its position
         self.mask = torch.full((1, 1, 1, max_len), float("-inf"), device=dev, dtype=dt)  # 0 where a key exists
@@ -393,6 +402,9 @@ class WhisperEngine:
         b, t, _ = enc.shape
         hd = self.d // self.heads_d
         for i, L in enumerate(self.dec_layers):
+            if self.cross_kv_views:
+                self.xkv[i].copy_(L["xkv"](enc))
+                continue
             k, v = L["xkv"](enc).split(self.d, dim=-1)
             self.k_cross[i].copy_(k.view(b, t, self.heads_d, hd).transpose(1, 2))
             self.v_cross[i].copy_(v.view(b, t, self.heads_d, hd).transpose(1, 2))
