@@ -234,7 +234,6 @@ gemm_a16_skinny_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_con
 #pragma unroll
             for (int j = 0; j < 32; ++j) __stcg(part + size_t(ch * 32 + j) * 128, __uint_as_float(r[j]));
           }
-          __threadfence();
         }
       }
     }
@@ -245,14 +244,16 @@ gemm_a16_skinny_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_con
   __syncthreads();
   if (p.ksplit > 1) {
     // the block that arrives last for its tile adds the parts; which block that is depends on timing, the
-    // order of the additions does not
+    // order of the additions does not.  Ordering as in a grid-wide barrier: the block's stores are ordered before
+    // thread 0's fence by the block barrier above, the fence is cumulative, and the last block's loads follow
+    // thread 0's second fence through the barrier below -- one thread fences, not 448 (1.5 % of a decode step).
     if (threadIdx.x == 0) {
       __threadfence();
       is_last = atomicAdd(p.counters + ft, 1u) == unsigned(p.ksplit - 1);
+      __threadfence();
     }
     __syncthreads();
     if (is_last) {
-      __threadfence();
       const int total = p.bt * 128;
       const float* part0 = p.partials + size_t(ft) * p.ksplit * total;
       // four features per thread and step, all parts' loads of a step in flight together: the reduction costs

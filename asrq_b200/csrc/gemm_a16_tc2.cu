@@ -354,15 +354,23 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         z2 = h2_as_u32(__half2half2(zh));
       }
       // the A slot must have been consumed by the MMAs of the K block that used it last (six blocks ago):
-      // their commit arrived on the slot's barrier in both CTAs.  Both barriers are tested in one go.
+      // their commit arrived on the slot's barrier in both CTAs.  Both barriers are tested in one go, the A slot's
+      // first.  The packed-weight slot's barrier is shared by the three groups in turn, and a parity test can only
+      // tell a phase from its neighbours: while the slot's PREVIOUS pass (eight K blocks ago, another group's) has not
+      // landed, the test for this pass reads "complete".  That pass has landed once this block's A slot is free (the
+      // MMAs of the block two after it are done), so the weight slot's test counts only if it was made after the A
+      // slot's test succeeded; otherwise it is made again.
       if (dpos == 0) T2_MARK(1, titer, 0);
       {
         const uint32_t got = tc::mbar_try_wait2(afree_bar(a), aph ^ 1u, wfull_bar(s), ph);
         bool okw = true;
-        if (!(got & 1u)) okw = tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7);
-        if (okw && !(got & 2u)) okw = tc::mbar_wait(wfull_bar(s), ph, p.status, 5);
-        // one decision for the warp (a wait that gave up ends the loop for all its lanes: the warp-wide operations
-        // below need every lane), and the lanes are together again from here on
+        if (!(got & 1u)) {
+          okw = tc::mbar_wait(afree_bar(a), aph ^ 1u, p.status, 7) && tc::mbar_wait(wfull_bar(s), ph, p.status, 5);
+        } else if (!(got & 2u)) {
+          okw = tc::mbar_wait(wfull_bar(s), ph, p.status, 5);
+        }
+        // one decision for the warp: a wait that gave up ends the loop for all its lanes (the warp barriers below
+        // need every lane).  Nothing below assumes that the lanes run in step after this vote.
         if (!__all_sync(0xffffffffu, okw)) break;
       }
       if (dpos == 0) T2_MARK(1, titer, 2);
@@ -370,14 +378,6 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
       uint4 qv[NV];
 #pragma unroll
       for (int v = 0; v < NV; ++v) qv[v] = tc::ld_shared_v4(base + w_ring + s * kT2WSlotBytes + t * (8 * BITS) + v * 16);
-      // The packed-weight slot is free once EVERY lane holds its words.  The lanes may have come out of the barrier
-      // waits above at different times (a lane that saw the phase complete in the combined test skips the waiting
-      // loop), so they are brought together and the arrival is made to depend on a warp-wide reduction over the words
-      // every lane loaded: it cannot be issued before all of those loads have returned.
-      {
-        const uint32_t dep = __reduce_or_sync(0xffffffffu, qv[0].x | qv[NV - 1].w);
-        if (lane == 0) tc::mbar_arrive_after(wfree_bar(s), dep);
-      }
       // 128-byte swizzle: 16-byte chunk c of row t lives at chunk position c ^ (t % 8); the row start is 128-byte
       // aligned, so the position is an XOR on the address
       const uint32_t arow = (base + a * kT2ATileBytes + t * 128) | uint32_t((t & 7) << 4);
@@ -397,6 +397,13 @@ gemm_a16_tc2_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_consta
         }
       }
       tc::fence_proxy_async_smem();
+      // The packed-weight slot is released only here, after the stores that consumed its words and behind a warp
+      // barrier: every lane has finished with the slot, whatever the lanes' relative progress was.  (Released right
+      // after the loads by lane 0, even behind a warp-wide reduction over the loaded words, the next TMA write into
+      // the slot was seen to land between the two 16-byte loads of lanes that ran behind lane 0: one K block of a few
+      // weight rows then held the codes of the block eight further on, once in some thousand launches.)
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(wfree_bar(s));
       arrive_on_leader(deq_bar(a), p.release_arrive != 0);
       if (dpos == 0) T2_MARK(1, titer, 3);
       ++titer;

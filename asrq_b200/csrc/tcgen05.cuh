@@ -56,16 +56,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait2(uint32_t bar_a, uint32_t pari
       : "memory");
   return got;
 }
-// Arrival that is issued only after `dep` (a value the caller loaded) is available.
-__device__ __forceinline__ void mbar_arrive_after(uint32_t bar, uint32_t dep) {
-  asm volatile(
-      "{\n\t.reg .u32 z;\n\t"
-      "and.b32 z, %1, 0;\n\t"
-      "add.u32 z, z, %0;\n\t"
-      "mbarrier.arrive.shared::cta.b64 _, [z];\n\t}" ::"r"(bar),
-      "r"(dep)
-      : "memory");
-}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");

@@ -330,6 +330,39 @@ def test_pair_kernel_bitwise_stress(release):
     asrq_b200.check_status()
 
 
+def test_pair_kernel_repeats_bit_for_bit_in_a_chain():
+    """The sequence of a transformer block's prefill at Qwen3-1.7B widths and M = 2560 (norm -> gate/up -> silu*up ->
+    down, the pair kernel launched behind other launches of the library), repeated: every repetition gives the bits
+    of the first, and those of the one-CTA kernel.  (With the packed-weight slot released before the warp had
+    provably finished reading it, one K block of a few weight rows was wrong about once in 300 such chains.)"""
+    m, h, inter = 2560, 2048, 6144
+    gen = torch.Generator().manual_seed(7)
+
+    def layer(n, k):
+        w = torch.randn(n, k, generator=gen) * 0.02
+        codes, scales, zeros, _ = O.rtn_codes(w, 4, 128, False)
+        return make_layer(dict(x=torch.zeros(1, k), weight=O.pack_codes(codes, 4), scales=scales.half(), zeros=zeros.half(),
+                               bias=None, bits=4, group_size=128))
+
+    import asrq_b200
+    gu, down = layer(2 * inter, h), layer(h, inter)
+    x = torch.randn(m, h, generator=gen).half().to(DEV)
+    g = torch.ones(h, dtype=torch.float16, device=DEV)
+
+    def chain():
+        hn = asrq_b200.add_rmsnorm(x, None, g, 1e-6)[1]
+        a = gu(hn)
+        return a, down(asrq_b200.silu_mul(a))
+
+    with lib_option("tc_pair", 0):
+        a0, d0 = [t.clone() for t in chain()]
+    for _ in range(150):
+        a, d = chain()
+        assert torch.equal(a, a0)
+        assert torch.equal(d, d0)
+    asrq_b200.check_status()
+
+
 def test_bf16_prefill_error_is_reported():
     """bf16 activations on the prefill kernel: the MMA takes bf16 weights, so every dequantised weight is
     rounded to 8 significand bits first.  On Whisper fc1 (K=1280 N=5120 M=1500) the result stays within
