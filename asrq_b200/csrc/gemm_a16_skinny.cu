@@ -203,12 +203,16 @@ gemm_a16_skinny_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_con
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(deq_bar(dgroup));
     }
+    ok = __all_sync(0xffffffffu, ok);  // a wait that gave up in any lane ends the warp's work
     if (dgroup == 0 && ok) {
       // ------------------------------ epilogue (warps 2-5: lane quadrants 2, 3, 0, 1) ------------------------------
       const int qd = warp & 3;
       const int f = ft * 128 + qd * 32 + lane;
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
-      if (tc::mbar_wait(accf_bar, 0u, p.status, 35)) {
+      // one decision for the warp, and the lanes together again after the polling loop: the tensor-memory loads
+      // below are warp-wide instructions
+      if (__all_sync(0xffffffffu, tc::mbar_wait(accf_bar, 0u, p.status, 35))) {
+        __syncwarp();
         tc::fence_after_sync();
         if (warp == 2 && lane == 0) SK_MARK(6);
         const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16);

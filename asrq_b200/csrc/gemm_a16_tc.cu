@@ -335,7 +335,10 @@ gemm_a16_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constan
       const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
       const int f = ft * 128 + qd * 32 + lane;
       const float bias = p.bias ? __half2float(__ldg(p.bias + f)) : 0.f;
-      if (!tc::mbar_wait(accf_bar(buf), aph, p.status, 6)) { ok = false; break; }
+      // one decision for the warp, and the lanes together again after the polling loop: the tensor-memory loads
+      // below are warp-wide instructions
+      if (!__all_sync(0xffffffffu, tc::mbar_wait(accf_bar(buf), aph, p.status, 6))) { ok = false; break; }
+      __syncwarp();
       tc::fence_after_sync();
       if (warp == 4 && lane == 0) mark(3, tcount, 0);
       const uint32_t taddr = tmem_base + (uint32_t(qd * 32) << 16) + buf * 256u;
